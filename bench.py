@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-KV decode path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # one rank per GPU under torchrun for N > 1
+    python bench.py --impl reference --gpus N --steps K --warmup W
+
+Workload (default ``serve``): the box-scale serving configuration -- 131,072 users over 8
+GPUs, i.e. 16,384 users per GPU, each with a quantized cache of 32 kv heads x 2,048 keys x
+128 dims (N(0,1) K/V through the codec), one bf16 query per user per step, 32 query heads.
+Per-GPU work is fixed, so N GPUs serve N x 16,384 users per step (weak scaling) and N = 8 is
+the configuration as stated.  A GPU keeps as many distinct users resident as fit in memory
+(``config.resident_users``); logical user u reads slot u mod resident_users, so every step
+still streams 16,384 x 9.18 MB from HBM (far larger than L2, no flush needed).
+
+One JSON line is printed by rank 0.  ``value`` is users/s with the query already on the
+device; ``e2e`` times the host-buffer C-ABI step (pinned host query in, pinned host result
+out, copies inside the timed region).  ``roofline`` relates the algorithmic bytes of one
+launch to the measured copy bandwidth in MEASURED_PEAKS.json.  ``cpu_baseline`` is the CPU
+oracle (a port of the reference's torch path) timed on a few users of the same shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+USERS_PER_GPU = 131072 // 8
+WORKLOADS = {
+    # name: (description, Hq, Hkv, S, users per GPU)
+    "serve": ("config4-box-serving-shard: 16384 users/GPU x 32 kv heads x 2048 keys, 1 bf16 query/user/step", 32, 32, 2048, USERS_PER_GPU),
+    "decode64": ("config1: 64 users x 8 heads x 50 keys", 8, 8, 50, 64),
+    "gqa": ("config2: 256 users, 32 q / 8 kv heads, context U[1024,8192]", 32, 8, 8192, 256),
+}
+BYTES_PER_KEY = 64 + 8 + 4 + 64          # K nibbles + K sign bytes + K norm + V nibbles
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per (user, kv head, key) of the decode kernel from the ncu capture summarised in
+# profiles/ (None until a capture exists); scaled to a full launch by the keys it processes.
+NCU_DRAM_BYTES_PER_KEY = None
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.thread.join(timeout=5)
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def build_resident_cache(dev, Hkv, S, n_res, seed, lens=None):
+    """Fill a resident packed cache with N(0,1) K/V pushed through the library's own
+    rotate+quantize kernel, chunk by chunk (set-up, untimed)."""
+    from omnistack_rs_b200.kernels.quantize import _quantize_into
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    cb = torch.tensor([-2.733, -2.069, -1.618, -1.256, -0.9424, -0.6568, -0.3881, -0.1284,
+                       0.1284, 0.3881, 0.6568, 0.9424, 1.256, 1.618, 2.069, 2.733], device=dev)  # 16-level Lloyd-Max, unit Gaussian
+    k_nib = torch.empty(n_res, Hkv, S, 64, dtype=torch.uint8, device=dev)
+    k_qjl = torch.empty(n_res, Hkv, S, 8, dtype=torch.uint8, device=dev)
+    k_norms = torch.empty(n_res, Hkv, S, dtype=torch.float32, device=dev)
+    v_nib = torch.empty(n_res, Hkv, S, 64, dtype=torch.uint8, device=dev)
+    chunk = max(1, min(n_res, (1 << 28) // (Hkv * S * 128)))          # <= 512 MiB of bf16 per chunk
+    sq = torch.empty(chunk, Hkv, S, 8, dtype=torch.uint8, device=dev)
+    sn = torch.empty(chunk, Hkv, S, dtype=torch.float32, device=dev)
+    for u0 in range(0, n_res, chunk):
+        n = min(chunk, n_res - u0)
+        x = torch.randn(n, Hkv, S, 128, generator=gen, device=dev, dtype=torch.bfloat16)
+        _quantize_into(x, cb, 0, True, k_nib[u0:u0 + n], k_qjl[u0:u0 + n], k_norms[u0:u0 + n], Hkv * S, S, None, 0)
+        x = torch.randn(n, Hkv, S, 128, generator=gen, device=dev, dtype=torch.bfloat16)
+        _quantize_into(x, cb, 0, True, v_nib[u0:u0 + n], sq[:n], sn[:n], Hkv * S, S, None, 0)
+    torch.cuda.synchronize(dev)
+    return k_nib, k_qjl, k_norms, v_nib, cb
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from omnistack_rs_b200 import _lib
+    from omnistack_rs_b200.kernels.fused_attention import _qattn
+    from omnistack_rs_b200.serving import HostDecodeStep
+
+    rank, world, local = dist_env()
+    if args.gpus != world and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    desc, Hq, Hkv, S, users = WORKLOADS[args.workload]
+    if args.users:
+        users = args.users
+    scale = 1.0 / math.sqrt(128)
+
+    # ---- resident cache ------------------------------------------------------------
+    bytes_per_user = Hkv * S * BYTES_PER_KEY
+    free, _total = torch.cuda.mem_get_info(dev)
+    budget = free - (20 << 30) if args.resident_users is None else None
+    n_res = args.resident_users or max(1, min(users, budget // bytes_per_user))
+    n_res = min(n_res, users)
+    lens = None
+    if args.workload == "gqa":
+        g = torch.Generator().manual_seed(1)
+        lens = torch.randint(1024, 8193, (users,), generator=g).to(torch.int32)
+    k_nib, k_qjl, k_norms, v_nib, cb = build_resident_cache(dev, Hkv, S, n_res, seed=1234 + rank)
+    slots = (torch.arange(users, dtype=torch.int32) % n_res).to(dev) if n_res < users else None
+    lens_dev = None if lens is None else lens.to(dev)
+    keys_per_step = int(lens.sum()) * Hkv if lens is not None else users * Hkv * S
+    alg_bytes = keys_per_step * BYTES_PER_KEY + users * Hq * (256 + 512)
+
+    n_q = 4
+    qs = [torch.randn(users, Hq, 1, 128, device=dev, dtype=torch.bfloat16) for _ in range(n_q)]
+
+    def step(i):
+        return _qattn(qs[i % n_q], k_nib, k_qjl, k_norms, v_nib, cb, 0, scale, True,
+                      seq_lens=lens_dev, cache_slots=slots, n_splits=args.splits)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident timing ------------------------------------------------------
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        out = step(i)
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    clocks = sampler.stop()
+    tmax = torch.tensor([ms_total], device=dev)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    ms_step = float(tmax) / args.steps
+    launches_per_step = 1 if (args.splits or 1) == 1 else 2
+    checksum = float(out.float().abs().mean())
+
+    # ---- end to end: host query in, host result out -----------------------------------
+    host = HostDecodeStep(k_nib, k_qjl, k_norms, v_nib, cb, n_heads=Hq, batch=users, q_dtype=torch.bfloat16,
+                          user_id=0, seq_lens=lens_dev, cache_slots=slots, scale=scale, n_chunks=args.chunks)
+    host.q_host.copy_(qs[0].cpu())
+    for _ in range(max(1, min(args.warmup, 3))):
+        host.step()
+    barrier()
+    e2e_steps = args.steps
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        res = host.step()
+    torch.cuda.synchronize(dev)
+    t1 = time.perf_counter()
+    e2e_t = torch.tensor([t1 - t0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_s_step = float(e2e_t) / e2e_steps
+    e2e_ok = bool(torch.equal(res, _qattn(qs[0], k_nib, k_qjl, k_norms, v_nib, cb, 0, scale, True,
+                                          seq_lens=lens_dev, cache_slots=slots, n_splits=1).cpu()))
+
+    # ---- CPU baseline: the oracle on a few users of the same shape (rank 0, N = 1) ------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(Hq, Hkv, S, lens, budget_s=args.cpu_seconds)
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peak()
+    achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+    line = {
+        "metric": "users_per_sec_quantized_kv_decode", "value": users * world / (ms_step * 1e-3), "unit": "users/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "users_per_gpu": users, "resident_users": n_res, "q_heads": Hq, "kv_heads": Hkv,
+                   "keys": S, "head_dim": 128, "bytes_per_key": BYTES_PER_KEY, "splits": args.splits or 1,
+                   "l2": "inputs larger than L2 (resident cache %.1f GB per GPU)" % (n_res * bytes_per_user / 1e9),
+                   "parallelism": f"users sharded over {world} GPU(s), no collective on the data path"},
+        "kv_gb_per_s": achieved * world,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": peak_kind, "frac_of_8000_nominal": achieved / 8000.0,
+                     "traffic": (NCU_DRAM_BYTES_PER_KEY * keys_per_step if NCU_DRAM_BYTES_PER_KEY else None),
+                     "algorithmic_bytes_per_launch": alg_bytes, "kernel": "qattn decode", "launch_ms": ms_step / launches_per_step},
+        "cpu_baseline": cpu,
+        "e2e": {"value": users * world / e2e_s_step, "unit": "users/s", "h2d_bytes_per_step": host.h2d_bytes,
+                "d2h_bytes_per_step": host.d2h_bytes, "ms_per_step": e2e_s_step * 1e3, "chunks": args.chunks,
+                "matches_device_path": e2e_ok},
+        "gpu_launches": args.steps * launches_per_step,
+        "clocks": clocks, "checksum": checksum,
+    }
+    print(json.dumps(line))
+
+
+def cpu_baseline(Hq, Hkv, S, lens, budget_s=15.0, n_users=2):
+    """Time the CPU oracle (port of the reference's torch path) on ``n_users`` users of the
+    workload's shape; repeated until about ``budget_s`` seconds have been spent."""
+    import oracle as orc
+    gen = torch.Generator().manual_seed(7)
+    Su = S if lens is None else int(lens[:n_users].max())
+    cb = orc.lloyd_max_fit(torch.randn(1 << 14, generator=gen), max_iters=20)
+    kn, kq, kr = orc.quantize_heads(orc.wht128(torch.randn(n_users, Hkv, Su, 128, generator=gen)), cb, 0)
+    vn, _, _ = orc.quantize_heads(orc.wht128(torch.randn(n_users, Hkv, Su, 128, generator=gen)), cb, 0)
+    q = torch.randn(n_users, Hq, 1, 128, generator=gen).to(torch.bfloat16)
+    orc.decode_attention(q, kn, kq, kr, vn, cb, 0)                      # warm-up
+    best, spent, reps = float("inf"), 0.0, 0
+    while spent < budget_s and reps < 50:
+        t0 = time.perf_counter()
+        orc.decode_attention(q, kn, kq, kr, vn, cb, 0)
+        dt = time.perf_counter() - t0
+        best, spent, reps = min(best, dt), spent + dt, reps + 1
+    return {"value": n_users / best, "unit": "users/s", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
+            "kind": "port", "sample": f"{n_users} users x {Hkv} kv heads x {Su} keys, best of {reps} calls of the CPU oracle"}
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU implementation of the path.  The reference is pure
+    Python and cannot be shipped to the GPU box, so the oracle port (pinned against it by
+    tests/golden) is what runs, with every host thread torch offers."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    import oracle as orc
+    desc, Hq, Hkv, S, users = WORKLOADS[args.workload]
+    n_users = args.ref_users
+    gen = torch.Generator().manual_seed(7)
+    cb = orc.lloyd_max_fit(torch.randn(1 << 14, generator=gen), max_iters=20)
+    kn, kq, kr = orc.quantize_heads(orc.wht128(torch.randn(n_users, Hkv, S, 128, generator=gen)), cb, 0)
+    vn, _, _ = orc.quantize_heads(orc.wht128(torch.randn(n_users, Hkv, S, 128, generator=gen)), cb, 0)
+    q = torch.randn(n_users, Hq, 1, 128, generator=gen).to(torch.bfloat16)
+    for _ in range(args.warmup):
+        orc.decode_attention(q, kn, kq, kr, vn, cb, 0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.decode_attention(q, kn, kq, kr, vn, cb, 0)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = n_users / dt
+    sample = f"each step = {n_users} users x {Hkv} kv heads x {S} keys through the CPU oracle (dequantise + fp32 attention)"
+    print(json.dumps({
+        "impl": "reference", "metric": "users_per_sec_quantized_kv_decode", "value": value, "unit": "users/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "users_per_step": n_users, "q_heads": Hq, "kv_heads": Hkv, "keys": S, "head_dim": 128},
+        "cpu_baseline": {"value": value, "unit": "users/s", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "users/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="serve", choices=sorted(WORKLOADS))
+    ap.add_argument("--users", type=int, default=None, help="users per GPU per step (default: the workload's)")
+    ap.add_argument("--resident-users", type=int, default=None, help="distinct users held in HBM (default: as many as fit)")
+    ap.add_argument("--splits", type=int, default=None, help="key-axis splits (default: chosen from the shape)")
+    ap.add_argument("--chunks", type=int, default=8, help="user chunks of the pipelined host-buffer step")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--ref-users", type=int, default=2, help="users per step of the reference arm")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,159 @@
+/*
+ * omni_b200 -- C ABI of the B200 (sm_100a) quantized-KV codec and fused decode attention.
+ *
+ * This is the boundary a host binding (ctypes, cffi, cgo ...) talks to.  Plain
+ * pointers and sizes only: no torch, no C++ types.  Each entry point names the
+ * routine of the OmniStack-RS reference (path inside that project : line) whose
+ * GPU work it replaces.
+ *
+ * Conventions
+ *   - every function returns an int32 status (OMNI_OK on success); a message for
+ *     the last failure on the calling thread is available from omni_last_error();
+ *   - pointers named *_dev / documented "device" are device addresses on the
+ *     device that is current when the call is made; the library never allocates or
+ *     frees caller-visible memory, it only owns the Rademacher tables that
+ *     omni_init() uploads;
+ *   - `stream` is a cudaStream_t passed as void*; calls are asynchronous with
+ *     respect to the host unless stated otherwise;
+ *   - a "row" is one 128-element (user, head, token) vector.  A packed row is
+ *     64 nibble bytes + 8 sign bytes + one fp32 norm, held in three arrays;
+ *   - the seed of the +-1 projection matrix of (user, head h) is
+ *     (user_id mod 1024) xor h, as in the reference (kernels/quantize.py:293-295,583).
+ */
+#ifndef OMNI_B200_H_
+#define OMNI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OMNI_HEAD_DIM   128
+#define OMNI_QJL_DIM    64
+#define OMNI_NIB_BYTES  64
+#define OMNI_QJL_BYTES  8
+#define OMNI_N_SEEDS    1024
+
+/* status codes */
+#define OMNI_OK               0
+#define OMNI_ERR_ARG          1   /* null pointer, negative size, misaligned buffer            */
+#define OMNI_ERR_UNSUPPORTED  2   /* shape outside what the kernels handle                      */
+#define OMNI_ERR_CUDA         3   /* CUDA runtime / launch error, see omni_last_error()         */
+#define OMNI_ERR_DEVICE_WAIT  4   /* a bounded device-side wait expired (status word non-zero)  */
+#define OMNI_ERR_NOT_INIT     5   /* omni_init() has not been called for the current device     */
+
+/* element types of floating-point inputs */
+#define OMNI_F32   0
+#define OMNI_BF16  1
+#define OMNI_F16   2
+
+/* Library life cycle.  omni_init builds the 1024-seed Rademacher tables on the host
+ * with MT19937 (the CPU generator behind torch.Generator, which the reference draws
+ * G from: kernels/quantize.py:410-414) and uploads them to `device`.  Idempotent. */
+int32_t omni_init(int32_t device);
+int32_t omni_shutdown(void);
+const char* omni_last_error(void);
+int32_t omni_abi_version(void);
+
+/* Host-only: copy the bit-packed G rows of seeds [seed_begin, seed_begin+seed_count)
+ * to `out` (seed_count * 64 * 4 uint32; bit d of projection row i sits in word d/32,
+ * position d%32).  Replaces the per-call torch.randint of kernels/quantize.py:410-414. */
+int32_t omni_gtable_host(uint32_t* out, int32_t seed_begin, int32_t seed_count);
+
+/* Normalised 128-point Walsh-Hadamard rotation of n_rows contiguous rows
+ * (kernels/hadamard.py:51-85 `_wht_torch`, :155-191 `_wht_rotate`, :196 `rotate_queries`,
+ * :214 `rotate_kv_cache`).  x and y are device arrays of `dtype`; y may equal x. */
+int32_t omni_rotate(const void* x, void* y, int64_t n_rows, int32_t dtype, void* stream);
+
+/* INT4 Lloyd-Max + QJL codec over x[B][H][T][128] (kernels/quantize.py:542-590
+ * `quantize_heads`; with rotate != 0 it also applies the rotation first, i.e. the bake
+ * step quantize_heads(_wht_torch(x)) of scripts/run_criteo_benchmark.py:355,367, and
+ * with out_offsets / out_offset it appends into a preallocated cache).
+ *   x            device, element strides xs_b, xs_h, xs_t (last axis contiguous)
+ *   codebooks    device fp32, [H][16] when cb_per_head != 0, else [16]
+ *   user_ids     device int32[B] or NULL (then `user_id` is used for every b)
+ *   nib/qjl/norms device outputs; row index of (b,h,t) is
+ *                b*os_b + h*os_h + t + (out_offsets ? out_offsets[b] : out_offset)
+ *                and row r occupies nib[64 r .. ], qjl[8 r ..], norms[r]
+ *   out_offsets  device int64[B] or NULL                                               */
+int32_t omni_quantize_heads(const void* x, int32_t dtype, int32_t rotate,
+                            const float* codebooks, int32_t cb_per_head,
+                            const int32_t* user_ids, int32_t user_id,
+                            int64_t B, int32_t H, int64_t T,
+                            int64_t xs_b, int64_t xs_h, int64_t xs_t,
+                            uint8_t* nib, uint8_t* qjl, float* norms,
+                            int64_t os_b, int64_t os_h,
+                            const int64_t* out_offsets, int64_t out_offset,
+                            void* stream);
+
+/* Inverse codec to fp32 out[B][H][T][128] (kernels/quantize.py:593-640 `dequantize_heads`).
+ * Packed inputs use row strides is_b, is_h as above; with_qjl == 0 gives cb[code] only. */
+int32_t omni_dequantize_heads(const uint8_t* nib, const uint8_t* qjl, const float* norms,
+                              const float* codebooks, int32_t cb_per_head,
+                              const int32_t* user_ids, int32_t user_id,
+                              int64_t B, int32_t H, int64_t T,
+                              int64_t is_b, int64_t is_h, int32_t with_qjl,
+                              float* out, void* stream);
+
+/* Row-seeded codec (kernels/quantize.py:456-499 `quantize_rows`, :502-537
+ * `dequantize_rows`): row i of n_rows contiguous fp32 rows uses seed
+ * (user_id mod 1024) xor (base_head_idx + i).  One shared [16] codebook. */
+int32_t omni_quantize_rows(const float* x, const float* codebook, int32_t base_head_idx, int32_t user_id,
+                           int64_t n_rows, uint8_t* nib, uint8_t* qjl, float* norms, void* stream);
+int32_t omni_dequantize_rows(const uint8_t* nib, const uint8_t* qjl, const float* norms,
+                             const float* codebook, int32_t base_head_idx, int32_t user_id,
+                             int64_t n_rows, int32_t with_qjl, float* out, void* stream);
+
+/* Fused attention over the packed cache (kernels/fused_attention.py:90-291
+ * `_fused_attention_kernel`, :320 `_fused_attn_triton`, :471-565 `OmniAttention` /
+ * `omni_attn`; numerics follow the CPU path :435-466 `_fused_attn_python`).
+ *   q            device [B][Hq][T][128] of q_dtype, contiguous
+ *   k_nib,k_qjl,k_norms,v_nib  packed cache; row of (slot, kv head h, key s) is
+ *                slot*ks_b + h*ks_h + s, slot = cache_slots ? cache_slots[b] : b
+ *   seq_lens     device int32[B] or NULL (then every user has S keys); values are
+ *                clamped to [0, S]; a user with 0 keys gets a zero output row
+ *   scale        softmax scale (the reference default is 1/sqrt(128))
+ *   rotate_q / unrotate_out  fold the Walsh-Hadamard rotation into the query /
+ *                out of the result (both 0 reproduces the reference, which expects a
+ *                rotated q and returns the output in rotated space)
+ *   n_splits     >= 1 partitions of the key axis; with n_splits > 1 `workspace` must
+ *                hold omni_qattn_workspace_bytes(...) bytes of device scratch
+ *   out          device fp32 [B][Hq][T][128]
+ *   status_word  device int32 or NULL; set non-zero by the kernel if a bounded wait
+ *                expires (the kernels never trap)                                        */
+size_t  omni_qattn_workspace_bytes(int64_t B, int32_t Hq, int32_t T, int32_t n_splits);
+int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
+                          const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
+                          const uint8_t* v_nib,
+                          const float* codebooks, int32_t cb_per_head,
+                          const int32_t* user_ids, int32_t user_id,
+                          const int32_t* seq_lens, const int32_t* cache_slots,
+                          int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
+                          int64_t ks_b, int64_t ks_h,
+                          float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out,
+                          int32_t n_splits, void* workspace, size_t workspace_bytes,
+                          float* out, int32_t* status_word, void* stream);
+
+/* One decode step with HOST query / result buffers (the serving loop of
+ * scripts/run_criteo_benchmark.py:481-560, where q arrives per step and the cache is
+ * resident): copies q_host -> q_stage (device), runs omni_qattn_decode, copies the
+ * result out_stage (device) -> out_host, in `n_chunks` user chunks pipelined over
+ * two internal streams, and returns after everything has completed.  q_host/out_host
+ * should be page-locked.  Remaining arguments as in omni_qattn_decode (n_splits = 1). */
+int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, void* q_stage,
+                               const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
+                               const uint8_t* v_nib,
+                               const float* codebooks, int32_t cb_per_head,
+                               const int32_t* user_ids, int32_t user_id,
+                               const int32_t* seq_lens, const int32_t* cache_slots,
+                               int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
+                               int64_t ks_b, int64_t ks_h,
+                               float scale, int32_t with_qjl,
+                               float* out_stage, float* out_host, int32_t n_chunks);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMNI_B200_H_ */

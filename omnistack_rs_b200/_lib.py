@@ -1,0 +1,113 @@
+"""ctypes binding of ``libomni_b200.so`` (declared in ``include/omni_b200.h``).
+
+There is no CPU implementation behind this module: if the shared library is missing
+or a tensor is not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+
+OK, ERR_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT, ERR_NOT_INIT = range(6)
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+# name -> (restype, argtypes); mirrors include/omni_b200.h
+_i32, _i64, _f32, _vp, _sz = C.c_int32, C.c_int64, C.c_float, C.c_void_p, C.c_size_t
+SIGNATURES = {
+    "omni_init": (_i32, [_i32]),
+    "omni_shutdown": (_i32, []),
+    "omni_last_error": (C.c_char_p, []),
+    "omni_abi_version": (_i32, []),
+    "omni_gtable_host": (_i32, [_vp, _i32, _i32]),
+    "omni_rotate": (_i32, [_vp, _vp, _i64, _i32, _vp]),
+    "omni_quantize_heads": (_i32, [_vp, _i32, _i32, _vp, _i32, _vp, _i32, _i64, _i32, _i64, _i64, _i64, _i64,
+                                   _vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "omni_dequantize_heads": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _i32, _i64, _i32, _i64, _i64, _i64, _i32,
+                                     _vp, _vp]),
+    "omni_quantize_rows": (_i32, [_vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp]),
+    "omni_dequantize_rows": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp]),
+    "omni_qattn_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32]),
+    "omni_qattn_decode": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
+                                 _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
+                                 _vp, _sz, _vp, _vp, _vp]),
+    "omni_qattn_decode_host": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
+                                      _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _vp, _vp, _i32]),
+}
+
+_lock = threading.Lock()
+_lib = None
+_inited = set()
+
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "libomni_b200.so")
+
+
+def lib_path() -> str:
+    return LIB_PATH
+
+
+def load() -> C.CDLL:
+    """Load the shared library (never builds implicitly; see ``omnistack_rs_b200.build``)."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            path = lib_path()
+            if not os.path.exists(path):
+                raise RuntimeError(
+                    f"{path} is missing: build it with `python -m omnistack_rs_b200.build` "
+                    "(there is no CPU fallback for the omni_b200 kernels)")
+            lib = C.CDLL(path)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype, fn.argtypes = res, args
+            _lib = lib
+        return _lib
+
+
+_EXC = {ERR_ARG: ValueError, ERR_UNSUPPORTED: NotImplementedError, ERR_CUDA: RuntimeError,
+        ERR_DEVICE_WAIT: RuntimeError, ERR_NOT_INIT: RuntimeError}
+
+
+def check(status: int) -> None:
+    if status != OK:
+        msg = load().omni_last_error().decode("utf-8", "replace")
+        raise _EXC.get(status, RuntimeError)(f"omni_b200 status {status}: {msg}")
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    """All tensors must live on one CUDA device; returns it."""
+    dev = None
+    for x in tensors:
+        if x is None:
+            continue
+        if not x.is_cuda:
+            raise RuntimeError("omni_b200 runs on CUDA tensors only (no CPU fallback); got a tensor on "
+                               f"{x.device}")
+        if dev is None:
+            dev = x.device
+        elif x.device != dev:
+            raise ValueError(f"tensors on different devices: {dev} and {x.device}")
+    if dev is None:
+        raise ValueError("no tensor given")
+    return dev
+
+
+def ensure_init(device: torch.device) -> C.CDLL:
+    lib = load()
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _inited:
+        check(lib.omni_init(idx))
+        _inited.add(idx)
+    return lib
+
+
+def ptr(x):
+    return None if x is None else C.c_void_p(x.data_ptr())
+
+
+def stream_ptr(device: torch.device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)

@@ -1,0 +1,349 @@
+// Fused decode / short-prefill attention over the packed INT4 + QJL cache.
+//
+// Work unit: one warp per (user, query head, query token, key split).  Lane l walks
+// keys l, l+32, ... of its split with a private online-softmax state (max, sum, 128
+// accumulators); nothing crosses lanes until the final merge.  K and V are dequantised
+// in registers by a 16-entry codebook lookup in shared memory (16 words occupy 16
+// distinct banks, so any access pattern is conflict-free).  The QJL part of K is
+// applied as a score correction  norm * c * sum_i s_i (q . g_i)  with the 64 values
+// (q . g_i) computed once per work unit -- the same algebra as the reference kernel
+// (kernels/fused_attention.py:198-213, 260-276) but with G seeded per (user, kv head)
+// exactly as the codec does (kernels/quantize.py:583), which is what the reference's
+// CPU path (kernels/fused_attention.py:435-466) computes.
+#include "common.cuh"
+#include <mutex>
+
+namespace omni {
+
+struct AttnArgs {
+    const void* q; int q_dtype;
+    const uint8_t* k_nib; const uint8_t* k_qjl; const float* k_norms; const uint8_t* v_nib;
+    const float* codebooks; int cb_per_head;
+    const int32_t* user_ids; int32_t user_id;
+    const int32_t* seq_lens; const int32_t* cache_slots;
+    int64_t B; int Hq, Hkv, T; int64_t S; int64_t ks_b, ks_h;
+    float scale; int with_qjl, rotate_q, unrotate_out; int n_splits;
+    float* ws; float* out; const uint32_t* g_rows;
+};
+
+constexpr int kAttnWarps = 4;
+constexpr int kWsStride = 132;     // floats per partial: 128 accumulators, max, sum, 2 pad
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, m));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(kFullMask, v, m);
+    return v;
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(AttnArgs a) {
+    __shared__ __align__(16) float q_s[kAttnWarps][kHeadDim];
+    __shared__ __align__(16) float qg_s[kAttnWarps][kQjlDim];
+    __shared__ float cb_s[kAttnWarps][16];
+    const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
+    const int64_t work = (int64_t)blockIdx.x * kAttnWarps + wib;
+    const int64_t n_work = a.B * a.Hq * a.T * a.n_splits;
+    if (work >= n_work) return;
+    const int split = (int)(work % a.n_splits);
+    int64_t rest = work / a.n_splits;
+    const int64_t qrow = rest;                       // index into q / out: ((b*Hq + hq)*T + tq)
+    rest /= a.T;
+    const int hq = (int)(rest % a.Hq);
+    const int64_t b = rest / a.Hq;
+    const int hkv = hq / (a.Hq / a.Hkv);
+
+    // ---- prologue: query, codebook, q . g_i ------------------------------------
+    float qv[4];
+    Elem<DT>::load4(a.q, qrow * kHeadDim + 4 * lane, qv);
+    if (a.rotate_q) wht128_warp(qv, lane);
+    *reinterpret_cast<float4*>(&q_s[wib][4 * lane]) = make_float4(qv[0], qv[1], qv[2], qv[3]);
+    if (lane < 16) cb_s[wib][lane] = __ldg(a.codebooks + (a.cb_per_head ? hkv * 16 : 0) + lane);
+    __syncwarp();
+    if (a.with_qjl) {
+        const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
+        const uint4* grow = reinterpret_cast<const uint4*>(a.g_rows) + (size_t)seed_of(uid, hkv) * kQjlDim;
+        const uint4 g0 = __ldg(grow + lane), g1 = __ldg(grow + lane + 32);
+        const uint32_t w0[4] = {g0.x, g0.y, g0.z, g0.w};
+        const uint32_t w1[4] = {g1.x, g1.y, g1.z, g1.w};
+        float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+#pragma unroll 8
+            for (int j = 0; j < 32; ++j) {
+                const float qd = q_s[wib][w * 32 + j];
+                acc0 += ((w0[w] >> j) & 1u) ? qd : -qd;
+                acc1 += ((w1[w] >> j) & 1u) ? qd : -qd;
+            }
+        }
+        const float cs = kQjlCoef * a.scale;
+        qg_s[wib][lane] = acc0 * cs;
+        qg_s[wib][lane + 32] = acc1 * cs;
+    }
+    __syncwarp();
+
+    // ---- key range of this split -----------------------------------------------
+    int64_t len = a.seq_lens ? (int64_t)a.seq_lens[b] : a.S;
+    len = len < 0 ? 0 : (len > a.S ? a.S : len);
+    int64_t per = (len + a.n_splits - 1) / a.n_splits;
+    per = (per + 31) / 32 * 32;
+    const int64_t s0 = (int64_t)split * per;
+    const int64_t s1 = (s0 + per < len) ? s0 + per : len;
+    const int64_t slot = a.cache_slots ? (int64_t)a.cache_slots[b] : b;
+    const int64_t base_row = slot * a.ks_b + (int64_t)hkv * a.ks_h;
+
+    float m = -INFINITY, l = 0.f;
+    float O[kHeadDim];
+#pragma unroll
+    for (int d = 0; d < kHeadDim; ++d) O[d] = 0.f;
+    const float* qs = q_s[wib];
+    const float* cbs = cb_s[wib];
+
+    for (int64_t k = s0 + lane; k < s1; k += 32) {
+        const int64_t row = base_row + k;
+        const uint4* kp = reinterpret_cast<const uint4*>(a.k_nib + row * kNibBytes);
+        float dot = 0.f;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+            const uint4 wv = __ldg(kp + c4);
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const float4 qa = *reinterpret_cast<const float4*>(qs + c4 * 32 + wi * 8);
+                const float4 qb = *reinterpret_cast<const float4*>(qs + c4 * 32 + wi * 8 + 4);
+                const uint32_t w = ww[wi];
+                dot = fmaf(qa.x, cbs[w & 15], dot);
+                dot = fmaf(qa.y, cbs[(w >> 4) & 15], dot);
+                dot = fmaf(qa.z, cbs[(w >> 8) & 15], dot);
+                dot = fmaf(qa.w, cbs[(w >> 12) & 15], dot);
+                dot = fmaf(qb.x, cbs[(w >> 16) & 15], dot);
+                dot = fmaf(qb.y, cbs[(w >> 20) & 15], dot);
+                dot = fmaf(qb.z, cbs[(w >> 24) & 15], dot);
+                dot = fmaf(qb.w, cbs[(w >> 28) & 15], dot);
+            }
+        }
+        float score = dot * a.scale;
+        if (a.with_qjl) {
+            const uint2 sb = __ldg(reinterpret_cast<const uint2*>(a.k_qjl + row * kQjlBytes));
+            const float nrm = __ldg(a.k_norms + row);
+            float corr = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float g0 = qg_s[wib][i], g1 = qg_s[wib][i + 32];
+                corr += ((sb.x >> i) & 1u) ? g0 : -g0;
+                corr += ((sb.y >> i) & 1u) ? g1 : -g1;
+            }
+            score = fmaf(nrm, corr, score);
+        }
+        const float m_new = fmaxf(m, score);
+        const float p = expf(score - m_new);
+        if (m_new > m) {
+            const float alpha = expf(m - m_new);
+            l *= alpha;
+#pragma unroll
+            for (int d = 0; d < kHeadDim; ++d) O[d] *= alpha;
+            m = m_new;
+        }
+        l += p;
+        const uint4* vp = reinterpret_cast<const uint4*>(a.v_nib + row * kNibBytes);
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+            const uint4 wv = __ldg(vp + c4);
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const uint32_t w = ww[wi];
+#pragma unroll
+                for (int n = 0; n < 8; ++n)
+                    O[c4 * 32 + wi * 8 + n] = fmaf(p, cbs[(w >> (4 * n)) & 15], O[c4 * 32 + wi * 8 + n]);
+            }
+        }
+    }
+
+    // ---- merge the 32 lane states ------------------------------------------------
+    const float m_w = warp_max(m);
+    const float f = (m == -INFINITY) ? 0.f : expf(m - m_w);
+    const float l_w = warp_sum(l * f);
+#pragma unroll
+    for (int d = 0; d < kHeadDim; ++d) O[d] *= f;
+    // butterfly reduce-scatter: afterwards O[0..3] hold dims 4*lane .. 4*lane+3
+#pragma unroll
+    for (int half = 64, mk = 16; half >= 4; half >>= 1, mk >>= 1) {
+        const bool upper = (lane & mk) != 0;
+#pragma unroll
+        for (int j = 0; j < half; ++j) {
+            const float send = upper ? O[j] : O[j + half];
+            const float keep = upper ? O[j + half] : O[j];
+            O[j] = keep + __shfl_xor_sync(kFullMask, send, mk);
+        }
+    }
+    if (a.n_splits == 1) {
+        float o[4];
+        const float inv = l_w > 0.f ? 1.f / l_w : 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = O[k] * inv;
+        if (a.unrotate_out) wht128_warp(o, lane);
+        *reinterpret_cast<float4*>(a.out + qrow * kHeadDim + 4 * lane) = make_float4(o[0], o[1], o[2], o[3]);
+    } else {
+        float* w = a.ws + work * kWsStride;
+        *reinterpret_cast<float4*>(w + 4 * lane) = make_float4(O[0], O[1], O[2], O[3]);
+        if (lane == 0) { w[128] = m_w; w[129] = l_w; }
+    }
+}
+
+// Merge the per-split partial states of one (user, head, token): warp per output row.
+__global__ void __launch_bounds__(kAttnWarps * 32) qattn_combine_kernel(const float* ws, float* out, int64_t n_rows,
+                                                                        int n_splits, int unrotate_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = (int64_t)blockIdx.x * kAttnWarps + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const float* w = ws + r * n_splits * kWsStride;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, w[s * kWsStride + 128]);
+    float l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = w[s * kWsStride + 128];
+        const float f = (ms == -INFINITY) ? 0.f : expf(ms - m);
+        l += w[s * kWsStride + 129] * f;
+        const float4 v = *reinterpret_cast<const float4*>(w + s * kWsStride + 4 * lane);
+        o[0] = fmaf(v.x, f, o[0]); o[1] = fmaf(v.y, f, o[1]); o[2] = fmaf(v.z, f, o[2]); o[3] = fmaf(v.w, f, o[3]);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[k] *= inv;
+    if (unrotate_out) wht128_warp(o, lane);
+    *reinterpret_cast<float4*>(out + r * kHeadDim + 4 * lane) = make_float4(o[0], o[1], o[2], o[3]);
+}
+
+static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+static int32_t validate(const AttnArgs& a, size_t ws_bytes) {
+    OMNI_REQUIRE(a.B >= 0 && a.Hq > 0 && a.Hkv > 0 && a.T >= 0 && a.S >= 0, OMNI_ERR_ARG, "qattn: bad extent");
+    OMNI_REQUIRE(a.Hq % a.Hkv == 0, OMNI_ERR_ARG, "qattn: Hq=%d is not a multiple of Hkv=%d", a.Hq, a.Hkv);
+    OMNI_REQUIRE(a.Hkv <= kSeeds, OMNI_ERR_UNSUPPORTED, "qattn: Hkv=%d exceeds %d", a.Hkv, kSeeds);
+    OMNI_REQUIRE(a.n_splits >= 1 && a.n_splits <= 1024, OMNI_ERR_ARG, "qattn: n_splits=%d outside [1,1024]", a.n_splits);
+    if (a.B == 0 || a.T == 0) return OMNI_OK;
+    OMNI_REQUIRE(a.q && a.out && a.codebooks, OMNI_ERR_ARG, "qattn: NULL q/out/codebooks");
+    OMNI_REQUIRE(a.S == 0 || (a.k_nib && a.v_nib && (!a.with_qjl || (a.k_qjl && a.k_norms))), OMNI_ERR_ARG,
+                 "qattn: NULL cache buffer");
+    OMNI_REQUIRE(aligned(a.q, a.q_dtype == OMNI_F32 ? 16 : 8) && aligned(a.out, 16), OMNI_ERR_ARG, "qattn: q/out misaligned");
+    OMNI_REQUIRE(aligned(a.k_nib, 16) && aligned(a.v_nib, 16) && aligned(a.k_qjl, 8) && aligned(a.k_norms, 4),
+                 OMNI_ERR_ARG, "qattn: cache arrays must be 16-byte (nibbles) / 8-byte (sign bytes) aligned");
+    if (a.n_splits > 1) {
+        const size_t need = omni_qattn_workspace_bytes(a.B, a.Hq, a.T, a.n_splits);
+        OMNI_REQUIRE(a.ws && aligned(a.ws, 16) && ws_bytes >= need, OMNI_ERR_ARG,
+                     "qattn: workspace of %zu bytes needed for %d splits, got %zu", need, a.n_splits, ws_bytes);
+    }
+    return OMNI_OK;
+}
+
+static int32_t launch(const AttnArgs& a, cudaStream_t st) {
+    if (a.B == 0 || a.T == 0) return OMNI_OK;
+    const int64_t n_work = a.B * a.Hq * a.T * a.n_splits;
+    const int64_t blocks = (n_work + kAttnWarps - 1) / kAttnWarps;
+    OMNI_REQUIRE(blocks <= 0x7fffffffLL, OMNI_ERR_UNSUPPORTED, "qattn: %lld work units exceed one grid", (long long)n_work);
+    switch (a.q_dtype) {
+        case OMNI_F32:  qattn_lane_per_key_kernel<OMNI_F32><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(a); break;
+        case OMNI_BF16: qattn_lane_per_key_kernel<OMNI_BF16><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(a); break;
+        case OMNI_F16:  qattn_lane_per_key_kernel<OMNI_F16><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(a); break;
+        default: return set_error(OMNI_ERR_ARG, "qattn: unknown q dtype code %d", a.q_dtype);
+    }
+    OMNI_CUDA(cudaGetLastError());
+    if (a.n_splits > 1) {
+        const int64_t rows = a.B * a.Hq * a.T;
+        qattn_combine_kernel<<<(unsigned)((rows + kAttnWarps - 1) / kAttnWarps), kAttnWarps * 32, 0, st>>>(
+            a.ws, a.out, rows, a.n_splits, a.unrotate_out);
+        OMNI_CUDA(cudaGetLastError());
+    }
+    return OMNI_OK;
+}
+
+// Two internal streams + events per device for the host-buffer step.
+struct HostStepStreams { cudaStream_t s[2] = {nullptr, nullptr}; bool ready = false; };
+static HostStepStreams g_hs[kMaxDevices];
+static std::mutex g_hs_mutex;
+
+}  // namespace omni
+
+using namespace omni;
+
+extern "C" size_t omni_qattn_workspace_bytes(int64_t B, int32_t Hq, int32_t T, int32_t n_splits) {
+    if (n_splits <= 1 || B <= 0 || Hq <= 0 || T <= 0) return 0;
+    return (size_t)B * Hq * T * n_splits * kWsStride * sizeof(float);
+}
+
+extern "C" int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
+                                     const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
+                                     const uint8_t* v_nib, const float* codebooks, int32_t cb_per_head,
+                                     const int32_t* user_ids, int32_t user_id,
+                                     const int32_t* seq_lens, const int32_t* cache_slots,
+                                     int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
+                                     int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
+                                     int32_t rotate_q, int32_t unrotate_out, int32_t n_splits,
+                                     void* workspace, size_t workspace_bytes, float* out,
+                                     int32_t* status_word, void* stream) {
+    (void)status_word;   // this kernel has no device-side waits
+    const DeviceTables* tb = tables_for_current_device();
+    if (!tb) return OMNI_ERR_NOT_INIT;
+    AttnArgs a{q, q_dtype, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id, seq_lens,
+               cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
+               (float*)workspace, out, tb->rows};
+    int32_t st = validate(a, workspace_bytes);
+    if (st != OMNI_OK) return st;
+    return launch(a, (cudaStream_t)stream);
+}
+
+extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, void* q_stage,
+                                          const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
+                                          const uint8_t* v_nib, const float* codebooks, int32_t cb_per_head,
+                                          const int32_t* user_ids, int32_t user_id,
+                                          const int32_t* seq_lens, const int32_t* cache_slots,
+                                          int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
+                                          int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
+                                          float* out_stage, float* out_host, int32_t n_chunks) {
+    const DeviceTables* tb = tables_for_current_device();
+    if (!tb) return OMNI_ERR_NOT_INIT;
+    OMNI_REQUIRE(q_host && q_stage && out_stage && out_host, OMNI_ERR_ARG, "qattn_decode_host: NULL buffer");
+    OMNI_REQUIRE(n_chunks >= 1, OMNI_ERR_ARG, "qattn_decode_host: n_chunks < 1");
+    int dev = 0;
+    OMNI_CUDA(cudaGetDevice(&dev));
+    {
+        std::lock_guard<std::mutex> lk(g_hs_mutex);
+        if (!g_hs[dev].ready) {
+            OMNI_CUDA(cudaStreamCreateWithFlags(&g_hs[dev].s[0], cudaStreamNonBlocking));
+            OMNI_CUDA(cudaStreamCreateWithFlags(&g_hs[dev].s[1], cudaStreamNonBlocking));
+            g_hs[dev].ready = true;
+        }
+    }
+    const size_t qsz = q_dtype == OMNI_F32 ? 4 : 2;
+    const int64_t per = (B + n_chunks - 1) / n_chunks;
+    int c = 0;
+    for (int64_t b0 = 0; b0 < B; b0 += per, ++c) {
+        const int64_t nb = (b0 + per <= B) ? per : B - b0;
+        cudaStream_t st = g_hs[dev].s[c & 1];
+        const size_t qoff = (size_t)b0 * Hq * T * kHeadDim;
+        OMNI_CUDA(cudaMemcpyAsync((char*)q_stage + qoff * qsz, (const char*)q_host + qoff * qsz,
+                                  (size_t)nb * Hq * T * kHeadDim * qsz, cudaMemcpyHostToDevice, st));
+        // without a slot table user b reads cache block b: shift the cache base for the chunk
+        const int64_t row0 = cache_slots ? 0 : b0 * ks_b;
+        AttnArgs a{(const char*)q_stage + qoff * qsz, q_dtype,
+                   k_nib + row0 * kNibBytes, k_qjl ? k_qjl + row0 * kQjlBytes : nullptr,
+                   k_norms ? k_norms + row0 : nullptr, v_nib + row0 * kNibBytes,
+                   codebooks, cb_per_head, user_ids ? user_ids + b0 : nullptr, user_id,
+                   seq_lens ? seq_lens + b0 : nullptr, cache_slots ? cache_slots + b0 : nullptr,
+                   nb, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, 0, 0, 1, nullptr, out_stage + qoff, tb->rows};
+        int32_t stc = validate(a, 0);
+        if (stc == OMNI_OK) stc = launch(a, st);
+        if (stc != OMNI_OK) { cudaStreamSynchronize(g_hs[dev].s[0]); cudaStreamSynchronize(g_hs[dev].s[1]); return stc; }
+        OMNI_CUDA(cudaMemcpyAsync(out_host + qoff, out_stage + qoff, (size_t)nb * Hq * T * kHeadDim * sizeof(float),
+                                  cudaMemcpyDeviceToHost, st));
+    }
+    OMNI_CUDA(cudaStreamSynchronize(g_hs[dev].s[0]));
+    OMNI_CUDA(cudaStreamSynchronize(g_hs[dev].s[1]));
+    return OMNI_OK;
+}

@@ -1,0 +1,139 @@
+"""Fused attention over the packed INT4 + QJL cache on the GPU.
+
+Mirrors ``omnistack_rs/kernels/fused_attention.py`` of the reference: ``omni_attn`` (:537),
+``OmniAttention`` (:471, 15 positional arguments, backward returns ``None`` for each) and
+``make_g_matrix`` (:296) keep their signatures.  The result is float32 of shape
+``(B, n_heads, T, 128)`` like the reference's GPU path (:361).
+
+Numerics follow the reference's CPU path ``_fused_attn_python`` (:435-466): K = INT4 + QJL,
+V = INT4 only, G seeded per (user, kv head) with ``(user_id % 1024) ^ head`` exactly as
+the codec.  ``g_matrix`` is accepted for signature compatibility and not used: the
+reference's ``make_g_matrix`` draws all heads from one stream and therefore disagrees with
+its own codec for every head but the first.
+
+Additive keyword arguments: ``seq_lens`` (per-user valid length), ``rotate_q`` /
+``unrotate_out`` (fold the Hadamard rotation into the query / out of the result),
+``n_splits`` (split-K over the key axis; chosen automatically when ``None``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .hadamard import HEAD_DIM
+from .quantize import QJL_DIM, _NBYTES_NIBBLE, _NBYTES_QJL, _make_qjl_seed, _prep_codebooks, _user_args  # noqa: F401
+
+BLOCK_T: int = 16
+BLOCK_S: int = 64
+_SM_COUNT = 148
+
+
+def make_g_matrix(n_kv_heads: int, seed: int, device="cpu"):
+    """(G_lo, G_hi) int64 ``(n_kv_heads, 64)``: bits 0..63 / 64..127 of each projection row,
+    drawn from one MT19937 stream of shape (n_kv_heads, 64, 128) like the reference (:296-317)."""
+    gen = torch.Generator().manual_seed(seed)
+    bits = torch.randint(0, 2, (n_kv_heads, QJL_DIM, HEAD_DIM), generator=gen, dtype=torch.int64)
+    weights = torch.ones(64, dtype=torch.int64) << torch.arange(64, dtype=torch.int64)
+    g_lo = (bits[..., :64] * weights).sum(dim=-1)
+    g_hi = (bits[..., 64:] * weights).sum(dim=-1)
+    return g_lo.to(device), g_hi.to(device)
+
+
+def _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha):
+    """q[b] += alpha * ((x[b] @ A[idx]^T) @ B[idx]^T) reshaped to heads; idx < 0 leaves the
+    row untouched (reference :401-430).  Batched on the device; returns float32."""
+    B, Hq, T, D = q.shape
+    idx = lora_indices.to(device=q.device, dtype=torch.long)
+    active = (idx >= 0)
+    safe = idx.clamp(min=0)
+    a = lora_a.to(q.device).float()[safe]                      # (B, rank, hidden)
+    bm = lora_b.to(q.device).float()[safe]                     # (B, Hq*D, rank)
+    down = torch.bmm(x.to(q.device).float(), a.transpose(1, 2))  # (B, T, rank)
+    up = torch.bmm(down, bm.transpose(1, 2))                   # (B, T, Hq*D)
+    delta = up.reshape(B, T, Hq, D).permute(0, 2, 1, 3) * float(lora_alpha)
+    return torch.where(active.view(B, 1, 1, 1), q.float() + delta, q.float())
+
+
+def _auto_splits(B: int, Hq: int, T: int, S: int) -> int:
+    """Enough (user, head, token, split) units to fill the GPU a few times over."""
+    units = B * Hq * T
+    target = _SM_COUNT * 16 * 2
+    if units >= target or S <= 256:
+        return 1
+    return int(max(1, min(target // max(units, 1), S // 128, 64)))
+
+
+def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
+           seq_lens=None, cache_slots=None, rotate_q=False, unrotate_out=False, n_splits=None):
+    dev = _lib.require_cuda(q, k_nibbles, k_qjl, k_norms, v_nibbles)
+    lib = _lib.ensure_init(dev)
+    B, Hq, T, D = q.shape
+    if D != HEAD_DIM:
+        raise ValueError(f"attention requires last dim = {HEAD_DIM} (head_dim), got {D}")
+    n_slots, Hkv, S, _ = k_nibbles.shape
+    if Hq % Hkv:
+        raise ValueError(f"n_heads={Hq} is not a multiple of n_kv_heads={Hkv}")
+    if cache_slots is None and n_slots != B:
+        raise ValueError(f"cache holds {n_slots} users but q has batch {B}")
+    if q.dtype not in _lib.DTYPE_CODE:
+        raise TypeError(f"unsupported q dtype {q.dtype}")
+    q = q.contiguous()
+    k_nibbles, k_qjl, v_nibbles = k_nibbles.contiguous(), k_qjl.contiguous(), v_nibbles.contiguous()
+    k_norms = k_norms.contiguous().float()
+    cb, per_head = _prep_codebooks(codebooks, Hkv, dev)
+    ids, uid = _user_args(user_id, B, dev)
+    lens = None if seq_lens is None else seq_lens.to(device=dev, dtype=torch.int32).contiguous()
+    slots = None if cache_slots is None else cache_slots.to(device=dev, dtype=torch.int32).contiguous()
+    if n_splits is None:
+        n_splits = _auto_splits(B, Hq, T, S)
+    ws, ws_bytes = None, 0
+    if n_splits > 1:
+        ws_bytes = lib.omni_qattn_workspace_bytes(B, Hq, T, n_splits)
+        ws = torch.empty(ws_bytes // 4, dtype=torch.float32, device=dev)
+    out = torch.empty(B, Hq, T, HEAD_DIM, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.omni_qattn_decode(
+            _lib.ptr(q), _lib.DTYPE_CODE[q.dtype], _lib.ptr(k_nibbles), _lib.ptr(k_qjl), _lib.ptr(k_norms),
+            _lib.ptr(v_nibbles), _lib.ptr(cb), per_head, _lib.ptr(ids), uid, _lib.ptr(lens), _lib.ptr(slots),
+            B, Hq, Hkv, T, S, Hkv * S, S, float(scale), int(bool(with_qjl)), int(bool(rotate_q)),
+            int(bool(unrotate_out)), int(n_splits), _lib.ptr(ws), ws_bytes, _lib.ptr(out), None,
+            _lib.stream_ptr(dev)))
+    return out
+
+
+class OmniAttention(torch.autograd.Function):
+    """Forward-only wrapper with the reference's argument list (inference path: the
+    backward returns ``None`` for all 15 inputs, reference :530-534)."""
+
+    @staticmethod
+    def forward(ctx, q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
+                g_matrix=None, x=None, lora_a=None, lora_b=None, lora_indices=None, lora_alpha=1.0):
+        if scale is None:
+            scale = 1.0 / math.sqrt(HEAD_DIM)
+        q_eff = q if x is None else _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha)
+        out = _qattn(q_eff, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl)
+        ctx.save_for_backward(q, out)
+        ctx.scale, ctx.with_qjl = scale, with_qjl
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        return (None,) * 15
+
+
+def omni_attn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id=0, scale: Optional[float] = None,
+              with_qjl: bool = True, g_matrix=None, x=None, lora_a=None, lora_b=None, lora_indices=None,
+              lora_alpha: float = 1.0, *, seq_lens=None, cache_slots=None, rotate_q: bool = False,
+              unrotate_out: bool = False, n_splits: Optional[int] = None) -> torch.Tensor:
+    """Fused INT4 + QJL attention with the optional per-user LoRA query update."""
+    if seq_lens is None and cache_slots is None and not rotate_q and not unrotate_out and n_splits is None:
+        return OmniAttention.apply(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
+                                   g_matrix, x, lora_a, lora_b, lora_indices, lora_alpha)
+    if scale is None:
+        scale = 1.0 / math.sqrt(HEAD_DIM)
+    q_eff = q if x is None else _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha)
+    return _qattn(q_eff, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
+                  seq_lens, cache_slots, rotate_q, unrotate_out, n_splits)

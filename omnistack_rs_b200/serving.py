@@ -1,0 +1,151 @@
+"""Per-user cache container, user sharding across GPUs, and the host-buffer decode step.
+
+The reference has no cache object (its README lists a paged cache as planned) and no
+multi-GPU code; its serving loop (scripts/run_criteo_benchmark.py:481-560) keeps the packed
+tensors resident on one GPU and sends a fresh query per step.  This module provides the same
+loop for one process per GPU: users are independent, so rank r of n simply owns a contiguous
+block of users and no collective is needed on the data path.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .kernels.quantize import _NBYTES_NIBBLE, _NBYTES_QJL, _prep_codebooks, rotate_quantize_append
+from .kernels.fused_attention import _qattn
+
+HEAD_DIM = 128
+
+
+def shard_range(n_units: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous block [begin, end) of ``n_units`` owned by ``rank``; the first
+    ``n_units % world_size`` ranks get one extra unit."""
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} outside world of {world_size}")
+    base, extra = divmod(n_units, world_size)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def gather_rows_to_rank0(local: torch.Tensor, n_units: int, group=None) -> Optional[torch.Tensor]:
+    """Gather per-rank row blocks (sharded with :func:`shard_range`) to rank 0 in user order.
+    Blocks are padded to a common height because ``gather`` needs equal shapes.  Returns the
+    ``(n_units, ...)`` tensor on rank 0 and ``None`` elsewhere.  Verification only -- the
+    data path itself has no collective."""
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    spans = [shard_range(n_units, world, r) for r in range(world)]
+    height = max(e - b for b, e in spans)
+    padded = local.new_zeros((height,) + tuple(local.shape[1:]))
+    padded[: local.shape[0]] = local
+    bufs = [torch.empty_like(padded) for _ in range(world)] if rank == 0 else None
+    dist.gather(padded, bufs, dst=0, group=group)
+    if rank != 0:
+        return None
+    return torch.cat([buf[: e - b] for buf, (b, e) in zip(bufs, spans)])
+
+
+class QuantizedKVCache:
+    """Preallocated packed K/V cache for ``n_users`` users on one device.
+
+    K rows hold nibbles + sign bytes + norm (4.75 bits per element); V rows are stored the
+    same way (the codec produces all three) although attention reads only V's nibbles.
+    """
+
+    def __init__(self, n_users: int, n_kv_heads: int, max_len: int, codebooks: torch.Tensor,
+                 device, user_ids: Optional[torch.Tensor] = None, store_v_residual: bool = True):
+        self.device = torch.device(device)
+        self.n_users, self.n_kv_heads, self.max_len = n_users, n_kv_heads, max_len
+        self.codebooks = codebooks.to(device=self.device, dtype=torch.float32).contiguous()
+        shape = (n_users, n_kv_heads, max_len)
+        mk = lambda *s, dt=torch.uint8: torch.zeros(*s, dtype=dt, device=self.device)  # noqa: E731
+        self.k_nib, self.k_qjl, self.k_norms = mk(*shape, _NBYTES_NIBBLE), mk(*shape, _NBYTES_QJL), mk(*shape, dt=torch.float32)
+        self.v_nib = mk(*shape, _NBYTES_NIBBLE)
+        if store_v_residual:
+            self.v_qjl, self.v_norms = mk(*shape, _NBYTES_QJL), mk(*shape, dt=torch.float32)
+        else:   # scratch rows shared by every append (attention never reads them)
+            self.v_qjl = self.v_norms = None
+        self.lens = torch.zeros(n_users, dtype=torch.int64, device=self.device)
+        self.user_ids = (torch.arange(n_users, dtype=torch.int32, device=self.device) if user_ids is None
+                         else user_ids.to(device=self.device, dtype=torch.int32).contiguous())
+
+    def bytes_per_key(self) -> int:
+        return 2 * (_NBYTES_NIBBLE + _NBYTES_QJL + 4) if self.v_qjl is not None else 2 * _NBYTES_NIBBLE + _NBYTES_QJL + 4
+
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor, rotate: bool = True) -> None:
+        """Quantize-append ``(n_users, n_kv_heads, T_new, 128)`` keys and values for every
+        user at its current length."""
+        T = k_new.shape[2]
+        if int(self.lens.max()) + T > self.max_len:
+            raise ValueError("append would run past the cache capacity")
+        rotate_quantize_append(k_new, self.k_nib, self.k_qjl, self.k_norms, self.lens, self.codebooks,
+                               self.user_ids, rotate=rotate)
+        if self.v_qjl is not None:
+            rotate_quantize_append(v_new, self.v_nib, self.v_qjl, self.v_norms, self.lens, self.codebooks,
+                                   self.user_ids, rotate=rotate)
+        else:
+            vq = torch.empty(self.n_users, self.n_kv_heads, self.max_len, _NBYTES_QJL, dtype=torch.uint8, device=self.device)
+            vn = torch.empty(self.n_users, self.n_kv_heads, self.max_len, dtype=torch.float32, device=self.device)
+            rotate_quantize_append(v_new, self.v_nib, vq, vn, self.lens, self.codebooks, self.user_ids, rotate=rotate)
+        self.lens += T
+
+    def attend(self, q: torch.Tensor, scale: Optional[float] = None, with_qjl: bool = True,
+               rotate_q: bool = False, unrotate_out: bool = False, n_splits: Optional[int] = None) -> torch.Tensor:
+        """Decode attention of ``q`` (n_users, n_heads, T, 128) against each user's valid prefix."""
+        if scale is None:
+            scale = 1.0 / math.sqrt(HEAD_DIM)
+        return _qattn(q, self.k_nib, self.k_qjl, self.k_norms, self.v_nib, self.codebooks, self.user_ids, scale,
+                      with_qjl, seq_lens=self.lens, rotate_q=rotate_q, unrotate_out=unrotate_out, n_splits=n_splits)
+
+
+class HostDecodeStep:
+    """One serving step with HOST buffers: query in page-locked host memory -> device,
+    fused attention over the resident cache, result back to page-locked host memory.  The
+    copies and kernels of consecutive user chunks overlap on two internal streams
+    (``omni_qattn_decode_host``).  The cache tensors must be complete before the first call
+    (the internal streams do not wait on the caller's stream)."""
+
+    def __init__(self, k_nib, k_qjl, k_norms, v_nib, codebooks, n_heads: int, batch: int, q_dtype=torch.bfloat16,
+                 user_id=0, seq_lens=None, cache_slots=None, scale: Optional[float] = None, with_qjl: bool = True,
+                 T: int = 1, n_chunks: int = 8):
+        self.dev = _lib.require_cuda(k_nib, k_qjl, k_norms, v_nib)
+        self.lib = _lib.ensure_init(self.dev)
+        self.k_nib, self.k_qjl, self.k_norms, self.v_nib = k_nib, k_qjl, k_norms, v_nib
+        n_slots, self.Hkv, self.S, _ = k_nib.shape
+        if cache_slots is None and n_slots != batch:
+            raise ValueError(f"cache holds {n_slots} users but the step batch is {batch}")
+        self.cb, self.per_head = _prep_codebooks(codebooks, self.Hkv, self.dev)
+        self.B, self.Hq, self.T, self.q_dtype = batch, n_heads, T, q_dtype
+        if isinstance(user_id, torch.Tensor):
+            self.ids, self.uid = user_id.to(device=self.dev, dtype=torch.int32).contiguous(), 0
+        else:
+            self.ids, self.uid = None, int(user_id) % 1024
+        self.lens = None if seq_lens is None else seq_lens.to(device=self.dev, dtype=torch.int32).contiguous()
+        self.slots = None if cache_slots is None else cache_slots.to(device=self.dev, dtype=torch.int32).contiguous()
+        self.scale = float(scale if scale is not None else 1.0 / math.sqrt(HEAD_DIM))
+        self.with_qjl, self.n_chunks = int(bool(with_qjl)), int(n_chunks)
+        shape = (batch, n_heads, T, HEAD_DIM)
+        self.q_stage = torch.empty(shape, dtype=q_dtype, device=self.dev)
+        self.out_stage = torch.empty(shape, dtype=torch.float32, device=self.dev)
+        self.q_host = torch.empty(shape, dtype=q_dtype).pin_memory()
+        self.out_host = torch.empty(shape, dtype=torch.float32).pin_memory()
+        self.h2d_bytes = self.q_host.numel() * self.q_host.element_size()
+        self.d2h_bytes = self.out_host.numel() * 4
+        torch.cuda.synchronize(self.dev)
+
+    def step(self, q_host: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs one step; returns the pinned host result tensor (overwritten by the next step)."""
+        src = self.q_host if q_host is None else q_host
+        if src.is_cuda or src.shape != self.q_host.shape or src.dtype != self.q_dtype or not src.is_contiguous():
+            raise ValueError("q_host must be a contiguous CPU tensor of the step's shape and dtype")
+        with torch.cuda.device(self.dev):
+            _lib.check(self.lib.omni_qattn_decode_host(
+                _lib.ptr(src), _lib.DTYPE_CODE[self.q_dtype], _lib.ptr(self.q_stage),
+                _lib.ptr(self.k_nib), _lib.ptr(self.k_qjl), _lib.ptr(self.k_norms), _lib.ptr(self.v_nib),
+                _lib.ptr(self.cb), self.per_head, _lib.ptr(self.ids), self.uid, _lib.ptr(self.lens), _lib.ptr(self.slots),
+                self.B, self.Hq, self.Hkv, self.T, self.S, self.Hkv * self.S, self.S, self.scale, self.with_qjl,
+                _lib.ptr(self.out_stage), _lib.ptr(self.out_host), self.n_chunks))
+        return self.out_host
