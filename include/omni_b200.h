@@ -136,6 +136,38 @@ int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
                           int32_t n_splits, void* workspace, size_t workspace_bytes,
                           float* out, int32_t* status_word, void* stream);
 
+/* Allocation-free decode attention.  No counterpart in the reference: it exists for hosts
+ * that must not allocate device memory when they call into this library -- an inference
+ * server or plugin host that owns the whole device heap and hands its plugins fixed
+ * buffers, or a latency-critical serving loop that cannot afford the device-wide
+ * synchronisation an allocation implies.  It is omni_qattn_decode with the split-K
+ * workspace (and a private copy of the Rademacher rows) held in arrays that are part of
+ * the library image, so neither this call nor any set-up it needs (omni_init included --
+ * it is not required here) calls cudaMalloc/cudaFree or an allocating library routine.
+ *   - the caller still passes every input and the output buffer;
+ *   - the scratch array is omni_qattn_noalloc_scratch_bytes() = 32 MiB, enough for
+ *     B*Hq*T*n_splits <= 63,550 partial states; larger requests return
+ *     OMNI_ERR_UNSUPPORTED with a message (n_splits == 1 needs no scratch and is never
+ *     rejected for size); every device that loads the library carries the 33 MiB until exit;
+ *   - the FIRST call on each device resolves the arrays' device addresses and uploads the
+ *     1 MiB row table with a blocking copy: make that call once, with the device current,
+ *     before any stream capture begins;
+ *   - all calls on a device share the one scratch array.  Every partial state a launch reads
+ *     is written by that same launch first, so stale contents of earlier calls are harmless,
+ *     but two calls whose kernels overlap on the GPU (different streams) race on it: keep
+ *     calls with n_splits > 1 on one stream or order them with events.                    */
+size_t  omni_qattn_noalloc_scratch_bytes(void);
+int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
+                                  const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
+                                  const uint8_t* v_nib,
+                                  const float* codebooks, int32_t cb_per_head,
+                                  const int32_t* user_ids, int32_t user_id,
+                                  const int32_t* seq_lens, const int32_t* cache_slots,
+                                  int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
+                                  int64_t ks_b, int64_t ks_h,
+                                  float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out,
+                                  int32_t n_splits, float* out, void* stream);
+
 /* One decode step with HOST query / result buffers (the serving loop of
  * scripts/run_criteo_benchmark.py:481-560, where q arrives per step and the cache is
  * resident): copies q_host -> q_stage (device), runs omni_qattn_decode, copies the

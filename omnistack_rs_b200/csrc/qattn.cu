@@ -268,6 +268,40 @@ struct HostStepStreams { cudaStream_t s[2] = {nullptr, nullptr}; bool ready = fa
 static HostStepStreams g_hs[kMaxDevices];
 static std::mutex g_hs_mutex;
 
+
+// ---- allocation-free variant ---------------------------------------------------------
+// Split-K scratch and a private copy of the Rademacher rows live in file-scope device
+// arrays, so the entry point below needs no device allocation at all.  The names of
+// these arrays are host-side handles, not device addresses: the address a kernel can use
+// comes from cudaGetSymbolAddress, taken once per device with that device current.
+constexpr size_t kStaticScratchBytes = 32u << 20;                       // 32 MiB of split-K partials
+constexpr size_t kStaticRowsWords = (size_t)kSeeds * kQjlDim * 4;        // 1 MiB of G rows
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+static __device__ __align__(256) uint32_t g_static_rows[kStaticRowsWords];
+
+struct StaticArrays { float* scratch = nullptr; uint32_t* rows = nullptr; };
+static StaticArrays g_static[kMaxDevices];
+static std::mutex g_static_mutex;
+
+// First use on the current device: resolve both symbol addresses and fill the G rows.
+static int32_t static_arrays_for_current_device(StaticArrays* out) {
+    int dev = -1;
+    OMNI_CUDA(cudaGetDevice(&dev));
+    OMNI_REQUIRE(dev >= 0 && dev < kMaxDevices, OMNI_ERR_ARG, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_static_mutex);
+    if (!g_static[dev].scratch) {
+        float* scratch = nullptr;
+        uint32_t* rows = nullptr;
+        OMNI_CUDA(cudaGetSymbolAddress((void**)&scratch, g_static_scratch));
+        OMNI_CUDA(cudaGetSymbolAddress((void**)&rows, g_static_rows));
+        OMNI_CUDA(cudaMemcpy(rows, host_rows_table(), kStaticRowsWords * sizeof(uint32_t), cudaMemcpyHostToDevice));
+        g_static[dev].rows = rows;
+        g_static[dev].scratch = scratch;
+    }
+    *out = g_static[dev];
+    return OMNI_OK;
+}
+
 }  // namespace omni
 
 using namespace omni;
@@ -346,4 +380,31 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
     OMNI_CUDA(cudaStreamSynchronize(g_hs[dev].s[0]));
     OMNI_CUDA(cudaStreamSynchronize(g_hs[dev].s[1]));
     return OMNI_OK;
+}
+
+extern "C" size_t omni_qattn_noalloc_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
+                                             const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
+                                             const uint8_t* v_nib, const float* codebooks, int32_t cb_per_head,
+                                             const int32_t* user_ids, int32_t user_id,
+                                             const int32_t* seq_lens, const int32_t* cache_slots,
+                                             int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
+                                             int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
+                                             int32_t rotate_q, int32_t unrotate_out, int32_t n_splits,
+                                             float* out, void* stream) {
+    const size_t need = omni_qattn_workspace_bytes(B, Hq, T, n_splits);
+    OMNI_REQUIRE(need <= kStaticScratchBytes, OMNI_ERR_UNSUPPORTED,
+                 "omni_qattn_decode_noalloc: B*Hq*T*n_splits = %lld partial states need %zu bytes of scratch but the "
+                 "built-in array holds %zu; lower n_splits or use omni_qattn_decode with a caller-provided workspace",
+                 (long long)(B * Hq * T * n_splits), need, kStaticScratchBytes);
+    StaticArrays arr;
+    int32_t st = static_arrays_for_current_device(&arr);
+    if (st != OMNI_OK) return st;
+    AttnArgs a{q, q_dtype, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id, seq_lens,
+               cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
+               arr.scratch, out, arr.rows};
+    st = validate(a, kStaticScratchBytes);
+    if (st != OMNI_OK) return st;
+    return launch(a, (cudaStream_t)stream);
 }
