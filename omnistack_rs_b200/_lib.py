@@ -51,7 +51,8 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "lib
 
 
 def lib_path() -> str:
-    return LIB_PATH
+    """Path of the shared library; OMNI_B200_LIB overrides the in-tree default."""
+    return os.environ.get("OMNI_B200_LIB", LIB_PATH)
 
 
 def load() -> C.CDLL:

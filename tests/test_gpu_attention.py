@@ -20,6 +20,15 @@ def dev():
     return torch.device("cuda:0")
 
 
+@pytest.fixture(autouse=True, params=["lane", "mma"])
+def kernel_choice(request, monkeypatch):
+    """Every case runs once per decode kernel: OMNI_QATTN_KERNEL forces the CUDA-core
+    lane-per-key kernel or the tensor-core kernel (which falls back by itself for shapes
+    it does not cover, e.g. more than 8 query columns per kv head)."""
+    monkeypatch.setenv("OMNI_QATTN_KERNEL", request.param)
+    return request.param
+
+
 def attn_mod():
     from omnistack_rs_b200.kernels import fused_attention
     return fused_attention
@@ -196,4 +205,4 @@ def test_serving_shape_slice_against_oracle(dev):
     # softmax weights sum to one: attending to a cache whose V rows are all one centroid returns it
     vn_const = torch.full_like(vn, 0x77)
     out_c = fa.omni_attn(*to_dev(dev, q, kn, kq, kr, vn_const, cb), user_id=0).cpu()
-    assert torch.allclose(out_c, torch.full_like(out_c, float(cb[7])), atol=1e-5)
+    assert torch.allclose(out_c, torch.full_like(out_c, float(cb[7])), atol=1e-3)   # fp16 centroids in the tensor-core kernel
