@@ -258,34 +258,46 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// first MMA of a chain: D = A*B with a zero addend (no accumulator registers to clear)
+__device__ __forceinline__ void mma_f16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     uint32_t d;
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
     return d;
 }
+#ifdef OMNI_LDG_L1ALLOC
+#define OMNI_LDG "ld.global.nc"
+#else
+#define OMNI_LDG "ld.global.nc.L1::no_allocate"
+#endif
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+    asm volatile(OMNI_LDG ".v4.u32 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 __device__ __forceinline__ uint2 ldg_stream8(const void* p) {
     uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    asm volatile(OMNI_LDG ".v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p));
     return v;
 }
 __device__ __forceinline__ uint32_t ldg_stream2(const void* p) {
     uint16_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];\n" : "=h"(v) : "l"(p));
+    asm volatile(OMNI_LDG ".u16 %0, [%1];\n" : "=h"(v) : "l"(p));
     return v;
 }
 __device__ __forceinline__ float ldg_stream_f32(const void* p) {
     float v;
-    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];\n" : "=f"(v) : "l"(p));
+    asm volatile(OMNI_LDG ".f32 %0, [%1];\n" : "=f"(v) : "l"(p));
     return v;
 }
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -302,7 +314,7 @@ template <int WHICH>
 __device__ __forceinline__ uint32_t lut_at(uint32_t lut_lane, uint32_t w) {
     const uint32_t addr = __byte_perm(w, lut_lane, 0x7604 | (WHICH << 4));
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));   // read-only table: free to be scheduled early
     return v;
 }
 // sign-table lookup: byte WHICH of the 16 sign bits selects four half2 of +-1.0
@@ -311,7 +323,7 @@ template <int WHICH>
 __device__ __forceinline__ uint4 sgn_at(uint32_t sgn_lane, uint32_t s) {
     const uint32_t addr = __byte_perm(s, sgn_lane, 0x7604 | (WHICH << 4));
     uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
 __host__ __device__ constexpr uint32_t sign_half2(uint32_t bit0, uint32_t bit1) {
@@ -319,19 +331,43 @@ __host__ __device__ constexpr uint32_t sign_half2(uint32_t bit0, uint32_t bit1) 
 }
 
 struct KeyBlock {           // packed bytes of one 16-key block as this thread needs them
-    uint4 ka, kb;           // K nibbles: key g and key g+8, bytes 16t..16t+15
-    uint2 v0, v1, v2, v3;   // V nibbles: keys 2t, 2t+1, 2t+8, 2t+9, bytes 8g..8g+7
-    uint32_t sa, sb;        // K sign bits: keys g, g+8, bits 16t..16t+15
-    float na, nb;           // K residual norms: keys g, g+8
+    // Score-tile row r of the MMA holds key rho(r): rho(g) = (g>>1) + 4*(g&1) for r < 8, rho(r) = rho(r-8)+8.
+    // With this order the transposed weights pair keys (t, t+4) and (t+8, t+12), so that each V load
+    // instruction reads four consecutive rows.
+    uint4 ka, kb;           // K nibbles: keys rho(g) and rho(g)+8, bytes 16t..16t+15
+    uint2 v0, v1, v2, v3;   // V nibbles: keys t, t+4, t+8, t+12, bytes 8g..8g+7
+    uint32_t sa, sb;        // K sign bits: keys rho(g), rho(g)+8, bits 16t..16t+15
+    float na, nb;           // K residual norms: keys rho(g), rho(g)+8
 };
 
 // Per-thread cursors into the packed arrays, positioned at the next block to load.
 struct Cursors {
-    const uint8_t* pk;      // k_nib + row(g)*64 + 16t
-    const uint8_t* pv;      // v_nib + row(2t)*64 + 8g
-    const uint8_t* ps;      // k_qjl + row(g)*8 + 2t
-    const float* pn;        // k_norms + row(g)
+    const uint8_t* pk;      // k_nib + row(rho(g))*64 + 16t
+    const uint8_t* pv;      // v_nib + row(t)*64 + 8g
+    const uint8_t* ps;      // k_qjl + row(rho(g))*8 + 2t
+    const float* pn;        // k_norms + row(rho(g))
+    const uint8_t* pf;      // L2 prefetch cursor of this lane (lanes 0-3: K nibbles, V nibbles, signs, norms)
+    const uint8_t* pf_end;  // end of this work unit's rows in that array: prefetches never reach past it
+    uint32_t pf_bytes;      // bytes per 16-key block behind pf (multiple of 16), 0 for the other lanes
 };
+
+constexpr int kPrefetchBlocks = 4;   // 16-key blocks between the L2 prefetch and the register loads
+
+// Bulk L2 prefetch (issued by the TMA unit): `bytes` (multiple of 16) from a 16-byte aligned address.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" :: "l"(p), "r"(bytes) : "memory");
+}
+// Block step j: the lane that owns stream (j mod 4) prefetches that stream for four blocks at once,
+// so every stream is refreshed every fourth block and stays kPrefetchBlocks..kPrefetchBlocks+3 ahead.
+__device__ __forceinline__ void prefetch_step(Cursors& c, int j, int lane) {
+    if (lane == (j & 3) && c.pf_bytes) {
+        const uint32_t room = (uint32_t)(c.pf_end - c.pf) & ~15u;
+        const uint32_t want = 4u * c.pf_bytes + 16u;                            // 16 extra: starts are rounded down
+        const uint32_t n = room < want ? room : want;
+        if (n) prefetch_l2_bulk(c.pf, n);
+        c.pf += 4u * c.pf_bytes;
+    }
+}
 
 // full block: every row exists, fixed offsets from the cursors
 template <bool QJL>
@@ -339,9 +375,9 @@ __device__ __forceinline__ void load_full_block(KeyBlock& kb, Cursors& c) {
     kb.ka = ldg_stream16(c.pk);
     kb.kb = ldg_stream16(c.pk + 8 * kNibBytes);
     kb.v0 = ldg_stream8(c.pv);
-    kb.v1 = ldg_stream8(c.pv + kNibBytes);
+    kb.v1 = ldg_stream8(c.pv + 4 * kNibBytes);
     kb.v2 = ldg_stream8(c.pv + 8 * kNibBytes);
-    kb.v3 = ldg_stream8(c.pv + 9 * kNibBytes);
+    kb.v3 = ldg_stream8(c.pv + 12 * kNibBytes);
     if (QJL) {
         kb.sa = ldg_stream2(c.ps);
         kb.sb = ldg_stream2(c.ps + 8 * kQjlBytes);
@@ -353,13 +389,13 @@ __device__ __forceinline__ void load_full_block(KeyBlock& kb, Cursors& c) {
 
 // last, partial block: rows past the end are clamped to the last valid key (their scores are masked)
 template <bool QJL>
-__device__ __forceinline__ void load_tail_block(KeyBlock& kb, const Cursors& c, int nvalid, int g, int t) {
+__device__ __forceinline__ void load_tail_block(KeyBlock& kb, const Cursors& c, int nvalid, int kl, int t) {
     const int last = nvalid - 1;
-    const int dg = min(g, last) - g, dg8 = min(g + 8, last) - g;
+    const int dg = min(kl, last) - kl, dg8 = min(kl + 8, last) - kl;
     kb.ka = ldg_stream16(c.pk + dg * kNibBytes);
     kb.kb = ldg_stream16(c.pk + dg8 * kNibBytes);
-    const int d0 = min(2 * t, last) - 2 * t, d1 = min(2 * t + 1, last) - 2 * t;
-    const int d2 = min(2 * t + 8, last) - 2 * t, d3 = min(2 * t + 9, last) - 2 * t;
+    const int d0 = min(t, last) - t, d1 = min(t + 4, last) - t;
+    const int d2 = min(t + 8, last) - t, d3 = min(t + 12, last) - t;
     kb.v0 = ldg_stream8(c.pv + d0 * kNibBytes);
     kb.v1 = ldg_stream8(c.pv + d1 * kNibBytes);
     kb.v2 = ldg_stream8(c.pv + d2 * kNibBytes);
@@ -377,50 +413,64 @@ struct WarpState {
     float m0, m1, l0, l1;   // running max (log2 units) and partial sums for columns 2t, 2t+1
 };
 
-template <bool QJL>
+constexpr float kLazyMaxSlack = 6.f;   // log2 units a score may exceed the reference maximum before it is raised
+
+
+template <bool QJL, bool TAIL>
 __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState& st, const uint32_t (&qB)[8][2],
                                                   const uint32_t (&gB)[4][2], float post0, float post1,
-                                                  uint32_t lut_lane, uint32_t sgn_lane, int nvalid, int g) {
-    float cd[4] = {0.f, 0.f, 0.f, 0.f};
+                                                  uint32_t lut_lane, uint32_t sgn_lane, int nvalid, int kl) {
+    // two independent accumulator chains per product so consecutive MMAs do not wait on each other
+    float cd[4], ce[4];
     {
         const uint32_t wa[4] = {kb.ka.x, kb.ka.y, kb.ka.z, kb.ka.w};
         const uint32_t wb[4] = {kb.kb.x, kb.kb.y, kb.kb.z, kb.kb.w};
+        // k-step 2w: bytes 0,1 of word w; k-step 2w+1: bytes 2,3
+        mma_f16_first(cd, lut_at<0>(lut_lane, wa[0]), lut_at<0>(lut_lane, wb[0]),
+                          lut_at<1>(lut_lane, wa[0]), lut_at<1>(lut_lane, wb[0]), qB[0][0], qB[0][1]);
+        mma_f16_first(ce, lut_at<2>(lut_lane, wa[0]), lut_at<2>(lut_lane, wb[0]),
+                          lut_at<3>(lut_lane, wa[0]), lut_at<3>(lut_lane, wb[0]), qB[1][0], qB[1][1]);
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            // k-step 2w: bytes 0,1 of word w; k-step 2w+1: bytes 2,3
+        for (int w = 1; w < 4; ++w) {
             mma_f16(cd, lut_at<0>(lut_lane, wa[w]), lut_at<0>(lut_lane, wb[w]),
                         lut_at<1>(lut_lane, wa[w]), lut_at<1>(lut_lane, wb[w]), qB[2 * w][0], qB[2 * w][1]);
-            mma_f16(cd, lut_at<2>(lut_lane, wa[w]), lut_at<2>(lut_lane, wb[w]),
+            mma_f16(ce, lut_at<2>(lut_lane, wa[w]), lut_at<2>(lut_lane, wb[w]),
                         lut_at<3>(lut_lane, wa[w]), lut_at<3>(lut_lane, wb[w]), qB[2 * w + 1][0], qB[2 * w + 1][1]);
         }
     }
-    float s00, s01, s80, s81;           // scores of key g / g+8 for columns 2t / 2t+1, log2 units
+    float s00, s01, s80, s81;           // scores of keys rho(g) / rho(g)+8 for columns 2t / 2t+1, log2 units
     if (QJL) {
-        float cq[4] = {0.f, 0.f, 0.f, 0.f};
+        float cq[4], cr[4];
         const uint4 a_lo = sgn_at<0>(sgn_lane, kb.sa), a_hi = sgn_at<1>(sgn_lane, kb.sa);   // key g
         const uint4 b_lo = sgn_at<0>(sgn_lane, kb.sb), b_hi = sgn_at<1>(sgn_lane, kb.sb);   // key g+8
-        mma_f16(cq, a_lo.x, b_lo.x, a_lo.y, b_lo.y, gB[0][0], gB[0][1]);
-        mma_f16(cq, a_lo.z, b_lo.z, a_lo.w, b_lo.w, gB[1][0], gB[1][1]);
+        mma_f16_first(cq, a_lo.x, b_lo.x, a_lo.y, b_lo.y, gB[0][0], gB[0][1]);
+        mma_f16_first(cr, a_lo.z, b_lo.z, a_lo.w, b_lo.w, gB[1][0], gB[1][1]);
         mma_f16(cq, a_hi.x, b_hi.x, a_hi.y, b_hi.y, gB[2][0], gB[2][1]);
-        mma_f16(cq, a_hi.z, b_hi.z, a_hi.w, b_hi.w, gB[3][0], gB[3][1]);
-        s00 = post0 * fmaf(kb.na, cq[0], cd[0]);
-        s01 = post1 * fmaf(kb.na, cq[1], cd[1]);
-        s80 = post0 * fmaf(kb.nb, cq[2], cd[2]);
-        s81 = post1 * fmaf(kb.nb, cq[3], cd[3]);
+        mma_f16(cr, a_hi.z, b_hi.z, a_hi.w, b_hi.w, gB[3][0], gB[3][1]);
+        s00 = post0 * fmaf(kb.na, cq[0] + cr[0], cd[0] + ce[0]);
+        s01 = post1 * fmaf(kb.na, cq[1] + cr[1], cd[1] + ce[1]);
+        s80 = post0 * fmaf(kb.nb, cq[2] + cr[2], cd[2] + ce[2]);
+        s81 = post1 * fmaf(kb.nb, cq[3] + cr[3], cd[3] + ce[3]);
     } else {
-        s00 = post0 * cd[0]; s01 = post1 * cd[1]; s80 = post0 * cd[2]; s81 = post1 * cd[3];
+        s00 = post0 * (cd[0] + ce[0]); s01 = post1 * (cd[1] + ce[1]);
+        s80 = post0 * (cd[2] + ce[2]); s81 = post1 * (cd[3] + ce[3]);
     }
-    if (g >= nvalid) { s00 = -INFINITY; s01 = -INFINITY; }
-    if (g + 8 >= nvalid) { s80 = -INFINITY; s81 = -INFINITY; }
-    // block maximum per column: over this thread's two keys, then over the 8 row groups
-    float mx0 = fmaxf(s00, s80), mx1 = fmaxf(s01, s81);
+    if (TAIL) {
+        if (kl >= nvalid) { s00 = -INFINITY; s01 = -INFINITY; }
+        if (kl + 8 >= nvalid) { s80 = -INFINITY; s81 = -INFINITY; }
+    }
+    // Lazy running maximum: the reference point m of a column is raised only when some score
+    // exceeds it by more than kLazyMaxSlack, so the cross-lane reduction and the rescale of the
+    // accumulators run on few blocks; in between, weights are at most 2^kLazyMaxSlack.
+    const bool exceed = (fmaxf(s00, s80) > st.m0 + kLazyMaxSlack) || (fmaxf(s01, s81) > st.m1 + kLazyMaxSlack);
+    if (__any_sync(kFullMask, exceed)) {
+        float mx0 = fmaxf(s00, s80), mx1 = fmaxf(s01, s81);
 #pragma unroll
-    for (int m = 4; m <= 16; m <<= 1) {
-        mx0 = fmaxf(mx0, __shfl_xor_sync(kFullMask, mx0, m));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(kFullMask, mx1, m));
-    }
-    const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
-    if (__any_sync(kFullMask, (mn0 > st.m0) || (mn1 > st.m1))) {
+        for (int m = 4; m <= 16; m <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(kFullMask, mx0, m));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(kFullMask, mx1, m));
+        }
+        const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
         const float al0 = ex2_approx(st.m0 - mn0), al1 = ex2_approx(st.m1 - mn1);
         st.l0 *= al0; st.l1 *= al1;
 #pragma unroll
@@ -463,6 +513,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) qattn_mma_kernel(AttnArgs a
     extern __shared__ __align__(1024) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const int kl = (g >> 1) + 4 * (g & 1);        // key (within a 16-key block) of score-tile row g
     const bool head_in_item = (gridDim.y == 1 && a.Hkv > 1);   // shared codebook: a CTA serves all kv heads
     const int cb_head = blockIdx.y;
     // place the table on a 64 KiB boundary of the shared window, the warp scratch beside it
@@ -580,25 +631,50 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) qattn_mma_kernel(AttnArgs a
         st.m0 = -INFINITY; st.m1 = -INFINITY; st.l0 = 0.f; st.l1 = 0.f;
 
         if (s1 > s0) {
-            const int64_t row_g = base_row + s0 + g, row_v = base_row + s0 + 2 * t;
-            Cursors cur{a.k_nib + row_g * kNibBytes + 16 * t, a.v_nib + row_v * kNibBytes + 8 * g,
-                        a.k_qjl + row_g * kQjlBytes + 2 * t, a.k_norms + row_g};
+            const int64_t row0 = base_row + s0;
+            const int64_t row_g = row0 + kl, row_v = row0 + t;
+            Cursors cur;
+            cur.pk = a.k_nib + row_g * kNibBytes + 16 * t;
+            cur.pv = a.v_nib + row_v * kNibBytes + 8 * g;
+            cur.ps = a.k_qjl + row_g * kQjlBytes + 2 * t;
+            cur.pn = a.k_norms + row_g;
             const int nfull = (int)((s1 - s0) >> 4), rem = (int)((s1 - s0) & 15);
-            const int nblk = nfull + (rem ? 1 : 0);
+            // L2 prefetch streams: lane 0 K nibbles, 1 V nibbles, 2 sign bytes, 3 norms.  The sign and
+            // norm rows need not start on a 16-byte boundary: round the start down and fetch 16 bytes more.
+            cur.pf = nullptr; cur.pf_end = nullptr; cur.pf_bytes = 0;
+            {
+                const int64_t nrows = s1 - s0;
+                if (lane == 0)             { cur.pf = a.k_nib + row0 * kNibBytes; cur.pf_bytes = 16 * kNibBytes; cur.pf_end = cur.pf + nrows * kNibBytes; }
+                else if (lane == 1)        { cur.pf = a.v_nib + row0 * kNibBytes; cur.pf_bytes = 16 * kNibBytes; cur.pf_end = cur.pf + nrows * kNibBytes; }
+                else if (QJL && lane == 2) { cur.pf = a.k_qjl + row0 * kQjlBytes; cur.pf_bytes = 16 * kQjlBytes; cur.pf_end = cur.pf + nrows * kQjlBytes; }
+                else if (QJL && lane == 3) { cur.pf = reinterpret_cast<const uint8_t*>(a.k_norms + row0); cur.pf_bytes = 16 * 4; cur.pf_end = cur.pf + nrows * 4; }
+            }
+            if (cur.pf_bytes) {
+                // the first blocks in one request, then one block per step
+                cur.pf = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(cur.pf) & ~(uintptr_t)15);
+                const uint32_t room = (uint32_t)(cur.pf_end - cur.pf) & ~15u;
+                // stream s is refreshed at block steps j = s (mod 4): start it s blocks further ahead
+                const uint32_t want = (kPrefetchBlocks + lane) * cur.pf_bytes + 16u;
+                const uint32_t n = room < want ? room : want;
+                if (n) prefetch_l2_bulk(cur.pf, n);
+                cur.pf += (kPrefetchBlocks + lane) * cur.pf_bytes;
+            }
             KeyBlock blk_a, blk_b;
-            // block j: full blocks advance the cursors; the partial block (always the last) does not need to
-            if (nfull > 0) load_full_block<QJL>(blk_a, cur); else load_tail_block<QJL>(blk_a, cur, rem, g, t);
-            for (int j = 0; j < nblk; j += 2) {
-                if (j + 1 < nblk) {
-                    if (j + 1 < nfull) load_full_block<QJL>(blk_b, cur); else load_tail_block<QJL>(blk_b, cur, rem, g, t);
-                }
-                process_key_block<QJL>(blk_a, st, qB, gB, post0, post1, lut_lane, sgn_lane, j < nfull ? 16 : rem, g);
-                if (j + 1 < nblk) {
-                    if (j + 2 < nblk) {
-                        if (j + 2 < nfull) load_full_block<QJL>(blk_a, cur); else load_tail_block<QJL>(blk_a, cur, rem, g, t);
-                    }
-                    process_key_block<QJL>(blk_b, st, qB, gB, post0, post1, lut_lane, sgn_lane, j + 1 < nfull ? 16 : rem, g);
-                }
+            if (nfull > 0) load_full_block<QJL>(blk_a, cur);
+            int j = 0;
+            for (; j + 1 < nfull; j += 2) {            // blocks j (in blk_a) and j+1 are full
+                load_full_block<QJL>(blk_b, cur);
+                prefetch_step(cur, j, lane);
+                process_key_block<QJL, false>(blk_a, st, qB, gB, post0, post1, lut_lane, sgn_lane, 16, kl);
+                if (j + 2 < nfull) load_full_block<QJL>(blk_a, cur);
+                prefetch_step(cur, j + 1, lane);
+                process_key_block<QJL, false>(blk_b, st, qB, gB, post0, post1, lut_lane, sgn_lane, 16, kl);
+            }
+            if (j < nfull)                              // odd count: the last full block is already in blk_a
+                process_key_block<QJL, false>(blk_a, st, qB, gB, post0, post1, lut_lane, sgn_lane, 16, kl);
+            if (rem) {                                   // partial block: clamped loads, masked scores
+                load_tail_block<QJL>(blk_b, cur, rem, kl, t);
+                process_key_block<QJL, true>(blk_b, st, qB, gB, post0, post1, lut_lane, sgn_lane, rem, kl);
             }
         }
 
