@@ -116,3 +116,24 @@ def ptr(x):
 
 def stream_ptr(device: torch.device):
     return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+_status_words = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word the kernels set when a bounded device-side wait expires."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[idx]
+
+
+def check_device_status(device: torch.device) -> None:
+    """Synchronises the device and raises if a kernel reported an expired wait since the last check."""
+    w = status_word(device)
+    torch.cuda.synchronize(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise RuntimeError(f"omni_b200: a device-side bounded wait expired (status {code})")

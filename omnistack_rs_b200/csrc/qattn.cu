@@ -10,36 +10,13 @@
 // (kernels/fused_attention.py:198-213, 260-276) but with G seeded per (user, kv head)
 // exactly as the codec does (kernels/quantize.py:583), which is what the reference's
 // CPU path (kernels/fused_attention.py:435-466) computes.
-#include "common.cuh"
+#include "qattn.cuh"
 #include <mutex>
 #include <cstdlib>
 
 namespace omni {
 
-struct AttnArgs {
-    const void* q; int q_dtype;
-    const uint8_t* k_nib; const uint8_t* k_qjl; const float* k_norms; const uint8_t* v_nib;
-    const float* codebooks; int cb_per_head;
-    const int32_t* user_ids; int32_t user_id;
-    const int32_t* seq_lens; const int32_t* cache_slots;
-    int64_t B; int Hq, Hkv, T; int64_t S; int64_t ks_b, ks_h;
-    float scale; int with_qjl, rotate_q, unrotate_out; int n_splits;
-    float* ws; float* out; const uint32_t* g_rows;
-};
-
 constexpr int kAttnWarps = 4;
-constexpr int kWsStride = 132;     // floats per partial: 128 accumulators, max, sum, 2 pad
-
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int m = 16; m >= 1; m >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, m));
-    return v;
-}
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(kFullMask, v, m);
-    return v;
-}
 
 template <int DT>
 __global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(AttnArgs a) {
@@ -222,497 +199,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) qattn_combine_kernel(const fl
 }
 
 
-// =====================================================================================
-// Tensor-core decode kernel (mma.sync m16n8k16, fp16 operands, fp32 accumulate).
-//
-// One warp owns one (user, kv head, key split) and all query columns of that kv head
-// (a column = one (query head of the group, query token); at most 8).  Keys are taken 16
-// at a time.  Everything is computed transposed so that the key axis is the MMA "M":
-//     S^T[key, col]  = sum_d  K^[key, d] * q[col, d]         (8 MMAs, A = dequantised K)
-//                    + norm[key] * sum_i s_i[key] * (q.g_i)[col]   (4 MMAs, A = +-1)
-//     O^T[d,  col]  += sum_key V^[key, d] * P[key, col]       (8 MMAs, A = dequantised V^T)
-// A fragments come straight from the packed bytes: a 256-entry table maps a byte to the
-// half2 (cb[low nibble], cb[high nibble]); it is replicated per lane so that every lookup
-// is bank-conflict free, and placed on a 64 KiB boundary of the shared window so that one
-// PRMT forms the complete address (byte -> bits 8..15).  The contraction index of each MMA
-// is a permutation of d (or of the projections) chosen so that each thread reads 16
-// contiguous bytes of a key row.  For V the two nibbles of a pair come from two different
-// keys; the index byte is formed with one shift and one LOP3 per four lookups.
-// Packed bytes go global -> registers (no shared-memory staging: shared-memory bandwidth
-// is what the table lookups need), double-buffered one 16-key block ahead.
-// =====================================================================================
-#ifndef OMNI_MMA_WARPS
-#define OMNI_MMA_WARPS 12
-#endif
-constexpr int kMmaWarps = OMNI_MMA_WARPS;
-constexpr int kLutSpan = 65536;                 // 256 entries x 256 B (32 lanes x 4 B used per entry)
-constexpr int kWarpScratchBytes = 512 + 8 * 64 * 4;
-// Dynamic shared memory: the two tables start at the first 64 KiB boundary of the shared
-// window (offset up to 65535 from the start of the allocation); the warp scratch sits in
-// front of them when that gap is large enough, otherwise behind them.
-constexpr int kScratchAllBytes = kMmaWarps * kWarpScratchBytes;
-constexpr int kMmaSmemBytes = (kLutSpan + 2 * kLutSpan) > (2 * kScratchAllBytes + 2 * kLutSpan)
-                                  ? (kLutSpan + 2 * kLutSpan) : (2 * kScratchAllBytes + 2 * kLutSpan);
-static_assert(kMmaSmemBytes <= 227 * 1024, "decode kernel exceeds the shared memory of one SM");
-constexpr float kLog2e = 1.4426950408889634f;
-
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                        uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// first MMA of a chain: D = A*B with a zero addend (no accumulator registers to clear)
-__device__ __forceinline__ void mma_f16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-}
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
-    uint32_t d;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
-    return d;
-}
-#ifdef OMNI_LDG_L1ALLOC
-#define OMNI_LDG "ld.global.nc"
-#else
-#define OMNI_LDG "ld.global.nc.L1::no_allocate"
-#endif
-__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
-    uint4 v;
-    asm volatile(OMNI_LDG ".v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint2 ldg_stream8(const void* p) {
-    uint2 v;
-    asm volatile(OMNI_LDG ".v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg_stream2(const void* p) {
-    uint16_t v;
-    asm volatile(OMNI_LDG ".u16 %0, [%1];\n" : "=h"(v) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ float ldg_stream_f32(const void* p) {
-    float v;
-    asm volatile(OMNI_LDG ".f32 %0, [%1];\n" : "=f"(v) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ float ex2_approx(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-// table lookup: byte `which` of w selects the entry; lut_lane has zero bits 8..15
-template <int WHICH>
-__device__ __forceinline__ uint32_t lut_at(uint32_t lut_lane, uint32_t w) {
-    const uint32_t addr = __byte_perm(w, lut_lane, 0x7604 | (WHICH << 4));
-    uint32_t v;
-    asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));   // read-only table: free to be scheduled early
-    return v;
-}
-// sign-table lookup: byte WHICH of the 16 sign bits selects four half2 of +-1.0
-// (bits 0,1 | 2,3 | 4,5 | 6,7 of that byte); sgn_lane has zero bits 8..15
-template <int WHICH>
-__device__ __forceinline__ uint4 sgn_at(uint32_t sgn_lane, uint32_t s) {
-    const uint32_t addr = __byte_perm(s, sgn_lane, 0x7604 | (WHICH << 4));
-    uint4 v;
-    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__host__ __device__ constexpr uint32_t sign_half2(uint32_t bit0, uint32_t bit1) {
-    return 0x3C003C00u ^ (bit0 ? 0u : 0x8000u) ^ (bit1 ? 0u : 0x80000000u);
-}
-
-struct KeyBlock {           // packed bytes of one 16-key block as this thread needs them
-    // Score-tile row r of the MMA holds key rho(r): rho(g) = (g>>1) + 4*(g&1) for r < 8, rho(r) = rho(r-8)+8.
-    // With this order the transposed weights pair keys (t, t+4) and (t+8, t+12), so that each V load
-    // instruction reads four consecutive rows.
-    uint4 ka, kb;           // K nibbles: keys rho(g) and rho(g)+8, bytes 16t..16t+15
-    uint2 v0, v1, v2, v3;   // V nibbles: keys t, t+4, t+8, t+12, bytes 8g..8g+7
-    uint32_t sa, sb;        // K sign bits: keys rho(g), rho(g)+8, bits 16t..16t+15
-    float na, nb;           // K residual norms: keys rho(g), rho(g)+8
-};
-
-// Per-thread cursors into the packed arrays, positioned at the next block to load.
-struct Cursors {
-    const uint8_t* pk;      // k_nib + row(rho(g))*64 + 16t
-    const uint8_t* pv;      // v_nib + row(t)*64 + 8g
-    const uint8_t* ps;      // k_qjl + row(rho(g))*8 + 2t
-    const float* pn;        // k_norms + row(rho(g))
-    const uint8_t* pf;      // L2 prefetch cursor of this lane (lanes 0-3: K nibbles, V nibbles, signs, norms)
-    const uint8_t* pf_end;  // end of this work unit's rows in that array: prefetches never reach past it
-    uint32_t pf_bytes;      // bytes per 16-key block behind pf (multiple of 16), 0 for the other lanes
-};
-
-constexpr int kPrefetchBlocks = 4;   // 16-key blocks between the L2 prefetch and the register loads
-
-// Bulk L2 prefetch (issued by the TMA unit): `bytes` (multiple of 16) from a 16-byte aligned address.
-__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" :: "l"(p), "r"(bytes) : "memory");
-}
-// Block step j: the lane that owns stream (j mod 4) prefetches that stream for four blocks at once,
-// so every stream is refreshed every fourth block and stays kPrefetchBlocks..kPrefetchBlocks+3 ahead.
-__device__ __forceinline__ void prefetch_step(Cursors& c, int j, int lane) {
-    if (lane == (j & 3) && c.pf_bytes) {
-        const uint32_t room = (uint32_t)(c.pf_end - c.pf) & ~15u;
-        const uint32_t want = 4u * c.pf_bytes + 16u;                            // 16 extra: starts are rounded down
-        const uint32_t n = room < want ? room : want;
-        if (n) prefetch_l2_bulk(c.pf, n);
-        c.pf += 4u * c.pf_bytes;
-    }
-}
-
-// full block: every row exists, fixed offsets from the cursors
-template <bool QJL>
-__device__ __forceinline__ void load_full_block(KeyBlock& kb, Cursors& c) {
-    kb.ka = ldg_stream16(c.pk);
-    kb.kb = ldg_stream16(c.pk + 8 * kNibBytes);
-    kb.v0 = ldg_stream8(c.pv);
-    kb.v1 = ldg_stream8(c.pv + 4 * kNibBytes);
-    kb.v2 = ldg_stream8(c.pv + 8 * kNibBytes);
-    kb.v3 = ldg_stream8(c.pv + 12 * kNibBytes);
-    if (QJL) {
-        kb.sa = ldg_stream2(c.ps);
-        kb.sb = ldg_stream2(c.ps + 8 * kQjlBytes);
-        kb.na = ldg_stream_f32(c.pn);
-        kb.nb = ldg_stream_f32(c.pn + 8);
-    }
-    c.pk += 16 * kNibBytes; c.pv += 16 * kNibBytes; c.ps += 16 * kQjlBytes; c.pn += 16;
-}
-
-// last, partial block: rows past the end are clamped to the last valid key (their scores are masked)
-template <bool QJL>
-__device__ __forceinline__ void load_tail_block(KeyBlock& kb, const Cursors& c, int nvalid, int kl, int t) {
-    const int last = nvalid - 1;
-    const int dg = min(kl, last) - kl, dg8 = min(kl + 8, last) - kl;
-    kb.ka = ldg_stream16(c.pk + dg * kNibBytes);
-    kb.kb = ldg_stream16(c.pk + dg8 * kNibBytes);
-    const int d0 = min(t, last) - t, d1 = min(t + 4, last) - t;
-    const int d2 = min(t + 8, last) - t, d3 = min(t + 12, last) - t;
-    kb.v0 = ldg_stream8(c.pv + d0 * kNibBytes);
-    kb.v1 = ldg_stream8(c.pv + d1 * kNibBytes);
-    kb.v2 = ldg_stream8(c.pv + d2 * kNibBytes);
-    kb.v3 = ldg_stream8(c.pv + d3 * kNibBytes);
-    if (QJL) {
-        kb.sa = ldg_stream2(c.ps + dg * kQjlBytes);
-        kb.sb = ldg_stream2(c.ps + dg8 * kQjlBytes);
-        kb.na = ldg_stream_f32(c.pn + dg);
-        kb.nb = ldg_stream_f32(c.pn + dg8);
-    }
-}
-
-struct WarpState {
-    float O[8][4];          // O^T accumulators: [m-tile][c-fragment]
-    float m0, m1, l0, l1;   // running max (log2 units) and partial sums for columns 2t, 2t+1
-};
-
-constexpr float kLazyMaxSlack = 6.f;   // log2 units a score may exceed the reference maximum before it is raised
-
-
-template <bool QJL, bool TAIL>
-__device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState& st, const uint32_t (&qB)[8][2],
-                                                  const uint32_t (&gB)[4][2], float post0, float post1,
-                                                  uint32_t lut_lane, uint32_t sgn_lane, int nvalid, int kl) {
-    // two independent accumulator chains per product so consecutive MMAs do not wait on each other
-    float cd[4], ce[4];
-    {
-        const uint32_t wa[4] = {kb.ka.x, kb.ka.y, kb.ka.z, kb.ka.w};
-        const uint32_t wb[4] = {kb.kb.x, kb.kb.y, kb.kb.z, kb.kb.w};
-        // k-step 2w: bytes 0,1 of word w; k-step 2w+1: bytes 2,3
-        mma_f16_first(cd, lut_at<0>(lut_lane, wa[0]), lut_at<0>(lut_lane, wb[0]),
-                          lut_at<1>(lut_lane, wa[0]), lut_at<1>(lut_lane, wb[0]), qB[0][0], qB[0][1]);
-        mma_f16_first(ce, lut_at<2>(lut_lane, wa[0]), lut_at<2>(lut_lane, wb[0]),
-                          lut_at<3>(lut_lane, wa[0]), lut_at<3>(lut_lane, wb[0]), qB[1][0], qB[1][1]);
-#pragma unroll
-        for (int w = 1; w < 4; ++w) {
-            mma_f16(cd, lut_at<0>(lut_lane, wa[w]), lut_at<0>(lut_lane, wb[w]),
-                        lut_at<1>(lut_lane, wa[w]), lut_at<1>(lut_lane, wb[w]), qB[2 * w][0], qB[2 * w][1]);
-            mma_f16(ce, lut_at<2>(lut_lane, wa[w]), lut_at<2>(lut_lane, wb[w]),
-                        lut_at<3>(lut_lane, wa[w]), lut_at<3>(lut_lane, wb[w]), qB[2 * w + 1][0], qB[2 * w + 1][1]);
-        }
-    }
-    float s00, s01, s80, s81;           // scores of keys rho(g) / rho(g)+8 for columns 2t / 2t+1, log2 units
-    if (QJL) {
-        float cq[4], cr[4];
-        const uint4 a_lo = sgn_at<0>(sgn_lane, kb.sa), a_hi = sgn_at<1>(sgn_lane, kb.sa);   // key g
-        const uint4 b_lo = sgn_at<0>(sgn_lane, kb.sb), b_hi = sgn_at<1>(sgn_lane, kb.sb);   // key g+8
-        mma_f16_first(cq, a_lo.x, b_lo.x, a_lo.y, b_lo.y, gB[0][0], gB[0][1]);
-        mma_f16_first(cr, a_lo.z, b_lo.z, a_lo.w, b_lo.w, gB[1][0], gB[1][1]);
-        mma_f16(cq, a_hi.x, b_hi.x, a_hi.y, b_hi.y, gB[2][0], gB[2][1]);
-        mma_f16(cr, a_hi.z, b_hi.z, a_hi.w, b_hi.w, gB[3][0], gB[3][1]);
-        s00 = post0 * fmaf(kb.na, cq[0] + cr[0], cd[0] + ce[0]);
-        s01 = post1 * fmaf(kb.na, cq[1] + cr[1], cd[1] + ce[1]);
-        s80 = post0 * fmaf(kb.nb, cq[2] + cr[2], cd[2] + ce[2]);
-        s81 = post1 * fmaf(kb.nb, cq[3] + cr[3], cd[3] + ce[3]);
-    } else {
-        s00 = post0 * (cd[0] + ce[0]); s01 = post1 * (cd[1] + ce[1]);
-        s80 = post0 * (cd[2] + ce[2]); s81 = post1 * (cd[3] + ce[3]);
-    }
-    if (TAIL) {
-        if (kl >= nvalid) { s00 = -INFINITY; s01 = -INFINITY; }
-        if (kl + 8 >= nvalid) { s80 = -INFINITY; s81 = -INFINITY; }
-    }
-    // Lazy running maximum: the reference point m of a column is raised only when some score
-    // exceeds it by more than kLazyMaxSlack, so the cross-lane reduction and the rescale of the
-    // accumulators run on few blocks; in between, weights are at most 2^kLazyMaxSlack.
-    const bool exceed = (fmaxf(s00, s80) > st.m0 + kLazyMaxSlack) || (fmaxf(s01, s81) > st.m1 + kLazyMaxSlack);
-    if (__any_sync(kFullMask, exceed)) {
-        float mx0 = fmaxf(s00, s80), mx1 = fmaxf(s01, s81);
-#pragma unroll
-        for (int m = 4; m <= 16; m <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(kFullMask, mx0, m));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(kFullMask, mx1, m));
-        }
-        const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
-        const float al0 = ex2_approx(st.m0 - mn0), al1 = ex2_approx(st.m1 - mn1);
-        st.l0 *= al0; st.l1 *= al1;
-#pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            st.O[mt][0] *= al0; st.O[mt][1] *= al1; st.O[mt][2] *= al0; st.O[mt][3] *= al1;
-        }
-        st.m0 = mn0; st.m1 = mn1;
-    }
-    const float p00 = ex2_approx(s00 - st.m0), p01 = ex2_approx(s01 - st.m1);
-    const float p80 = ex2_approx(s80 - st.m0), p81 = ex2_approx(s81 - st.m1);
-    st.l0 += p00 + p80;
-    st.l1 += p01 + p81;
-    // P^T as the B operand: transpose the two 8x8 (key x column) blocks across the warp
-    const uint32_t pb0 = movmatrix_trans(pack_half2(p00, p01));
-    const uint32_t pb1 = movmatrix_trans(pack_half2(p80, p81));
-    // V: index byte = nibble of key A | nibble of key B << 4
-    {
-        const uint32_t A[2] = {kb.v0.x, kb.v0.y}, B[2] = {kb.v1.x, kb.v1.y};
-        const uint32_t C[2] = {kb.v2.x, kb.v2.y}, D[2] = {kb.v3.x, kb.v3.y};
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t x01 = (A[h] & 0x0F0F0F0Fu) | ((B[h] << 4) & 0xF0F0F0F0u);
-            const uint32_t y01 = ((A[h] >> 4) & 0x0F0F0F0Fu) | (B[h] & 0xF0F0F0F0u);
-            const uint32_t x23 = (C[h] & 0x0F0F0F0Fu) | ((D[h] << 4) & 0xF0F0F0F0u);
-            const uint32_t y23 = ((C[h] >> 4) & 0x0F0F0F0Fu) | (D[h] & 0xF0F0F0F0u);
-            mma_f16(st.O[4 * h + 0], lut_at<0>(lut_lane, x01), lut_at<0>(lut_lane, y01),
-                                     lut_at<0>(lut_lane, x23), lut_at<0>(lut_lane, y23), pb0, pb1);
-            mma_f16(st.O[4 * h + 1], lut_at<1>(lut_lane, x01), lut_at<1>(lut_lane, y01),
-                                     lut_at<1>(lut_lane, x23), lut_at<1>(lut_lane, y23), pb0, pb1);
-            mma_f16(st.O[4 * h + 2], lut_at<2>(lut_lane, x01), lut_at<2>(lut_lane, y01),
-                                     lut_at<2>(lut_lane, x23), lut_at<2>(lut_lane, y23), pb0, pb1);
-            mma_f16(st.O[4 * h + 3], lut_at<3>(lut_lane, x01), lut_at<3>(lut_lane, y01),
-                                     lut_at<3>(lut_lane, x23), lut_at<3>(lut_lane, y23), pb0, pb1);
-        }
-    }
-}
-
-template <int DT, bool QJL>
-__global__ void __launch_bounds__(kMmaWarps * 32, 1) qattn_mma_kernel(AttnArgs a, int64_t n_items) {
-    extern __shared__ __align__(1024) unsigned char smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int kl = (g >> 1) + 4 * (g & 1);        // key (within a 16-key block) of score-tile row g
-    const bool head_in_item = (gridDim.y == 1 && a.Hkv > 1);   // shared codebook: a CTA serves all kv heads
-    const int cb_head = blockIdx.y;
-    // place the table on a 64 KiB boundary of the shared window, the warp scratch beside it
-    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t lut_off = (kLutSpan - (smem_base & (kLutSpan - 1))) & (kLutSpan - 1);
-    constexpr uint32_t kScratchAll = kMmaWarps * kWarpScratchBytes;
-    const uint32_t scratch_off = (lut_off >= kScratchAll) ? 0u : lut_off + 2 * kLutSpan;
-    {
-        const float* cb = a.codebooks + (a.cb_per_head ? cb_head * 16 : 0);
-        uint32_t* lut = reinterpret_cast<uint32_t*>(smem + lut_off);
-        for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
-            const int byte = i >> 5, ln = i & 31;
-            lut[byte * 64 + ln] = pack_half2(__ldg(cb + (byte & 15)), __ldg(cb + (byte >> 4)));
-        }
-        if (QJL) {   // sign table: entry b, 8 copies of 16 B: +-1.0 pairs for bits (0,1) (2,3) (4,5) (6,7) of b
-            uint4* sgn = reinterpret_cast<uint4*>(smem + lut_off + kLutSpan);
-            for (int i = threadIdx.x; i < 256 * 8; i += blockDim.x) {
-                const uint32_t b = i >> 3;
-                sgn[b * 16 + (i & 7)] = make_uint4(sign_half2(b & 1, b & 2), sign_half2(b & 4, b & 8),
-                                                   sign_half2(b & 16, b & 32), sign_half2(b & 64, b & 128));
-            }
-        }
-    }
-    __syncthreads();
-    const uint32_t lut_lane = smem_base + lut_off + 4 * lane;                     // bits 8..15 are zero
-    const uint32_t sgn_lane = smem_base + lut_off + kLutSpan + 16 * (lane & 7);  // likewise
-    float* qf = reinterpret_cast<float*>(smem + scratch_off + warp * kWarpScratchBytes);
-    float* qg_s = qf + 128;                                          // [8][64]
-    const int Gq = a.Hq / a.Hkv;
-    const int ncols = Gq * a.T;
-    const float qs = a.scale * kLog2e;
-
-    for (int64_t item = (int64_t)blockIdx.x * kMmaWarps + warp; item < n_items;
-         item += (int64_t)gridDim.x * kMmaWarps) {
-        int64_t rest = item;
-        int hkv = cb_head;
-        if (head_in_item) { hkv = (int)(rest % a.Hkv); rest /= a.Hkv; }
-        const int split = (int)(rest % a.n_splits);
-        const int64_t b = rest / a.n_splits;
-
-        // ---- prologue: B operands (scaled queries, q.g projections) ---------------------
-        uint32_t qB[8][2], gB[4][2];
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) { qB[kk][0] = 0u; qB[kk][1] = 0u; }
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) { gB[kk][0] = 0u; gB[kk][1] = 0u; }
-        float post0 = 1.f, post1 = 1.f;
-        uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0;
-        if (QJL) {
-            const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
-            const uint4* grow = reinterpret_cast<const uint4*>(a.g_rows) + (size_t)seed_of(uid, hkv) * kQjlDim;
-            g0 = __ldg(grow + lane); g1 = __ldg(grow + lane + 32);
-        }
-        for (int c = 0; c < ncols; ++c) {
-            const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + c / a.T) * a.T + (c % a.T);
-            float qv[4];
-            Elem<DT>::load4(a.q, qrow * kHeadDim + 4 * lane, qv);
-            const float mx = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3])))) * fabsf(qs);
-            // keep the fp16 operands below 2^10 in magnitude; the power of two is re-applied to the scores
-            float post = 1.f;
-            if (mx > 1024.f) post = exp2f(ceilf(log2f(mx * (1.f / 1024.f))));
-            const float f = qs / post;
-            __syncwarp();
-            *reinterpret_cast<float4*>(qf + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
-            __syncwarp();
-            if (QJL) {
-                const uint32_t w0[4] = {g0.x, g0.y, g0.z, g0.w}, w1[4] = {g1.x, g1.y, g1.z, g1.w};
-                float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-#pragma unroll 8
-                    for (int j = 0; j < 32; ++j) {
-                        const float qd = qf[w * 32 + j];
-                        acc0 += ((w0[w] >> j) & 1u) ? qd : -qd;
-                        acc1 += ((w1[w] >> j) & 1u) ? qd : -qd;
-                    }
-                }
-                qg_s[c * 64 + lane] = acc0 * (kQjlCoef * f);
-                qg_s[c * 64 + lane + 32] = acc1 * (kQjlCoef * f);
-            }
-            if (g == c) {
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const float4 v = *reinterpret_cast<const float4*>(qf + 32 * t + 4 * kk);
-                    qB[kk][0] = pack_half2(v.x * f, v.y * f);
-                    qB[kk][1] = pack_half2(v.z * f, v.w * f);
-                }
-            }
-            if (c == 2 * t) post0 = post;
-            if (c == 2 * t + 1) post1 = post;
-        }
-        __syncwarp();
-        if (QJL && g < ncols) {
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                const float4 v = *reinterpret_cast<const float4*>(qg_s + g * 64 + 16 * t + 4 * kk);
-                gB[kk][0] = pack_half2(v.x, v.y);
-                gB[kk][1] = pack_half2(v.z, v.w);
-            }
-        }
-
-        // ---- key range of this split -----------------------------------------------------
-        int64_t len = a.seq_lens ? (int64_t)a.seq_lens[b] : a.S;
-        len = len < 0 ? 0 : (len > a.S ? a.S : len);
-        int64_t per = (len + a.n_splits - 1) / a.n_splits;
-        per = (per + 31) / 32 * 32;
-        const int64_t s0 = (int64_t)split * per;
-        const int64_t s1 = (s0 + per < len) ? s0 + per : len;
-        const int64_t slot = a.cache_slots ? (int64_t)a.cache_slots[b] : b;
-        const int64_t base_row = slot * a.ks_b + (int64_t)hkv * a.ks_h;
-
-        WarpState st;
-#pragma unroll
-        for (int mt = 0; mt < 8; ++mt) { st.O[mt][0] = 0.f; st.O[mt][1] = 0.f; st.O[mt][2] = 0.f; st.O[mt][3] = 0.f; }
-        st.m0 = -INFINITY; st.m1 = -INFINITY; st.l0 = 0.f; st.l1 = 0.f;
-
-        if (s1 > s0) {
-            const int64_t row0 = base_row + s0;
-            const int64_t row_g = row0 + kl, row_v = row0 + t;
-            Cursors cur;
-            cur.pk = a.k_nib + row_g * kNibBytes + 16 * t;
-            cur.pv = a.v_nib + row_v * kNibBytes + 8 * g;
-            cur.ps = a.k_qjl + row_g * kQjlBytes + 2 * t;
-            cur.pn = a.k_norms + row_g;
-            const int nfull = (int)((s1 - s0) >> 4), rem = (int)((s1 - s0) & 15);
-            // L2 prefetch streams: lane 0 K nibbles, 1 V nibbles, 2 sign bytes, 3 norms.  The sign and
-            // norm rows need not start on a 16-byte boundary: round the start down and fetch 16 bytes more.
-            cur.pf = nullptr; cur.pf_end = nullptr; cur.pf_bytes = 0;
-            {
-                const int64_t nrows = s1 - s0;
-                if (lane == 0)             { cur.pf = a.k_nib + row0 * kNibBytes; cur.pf_bytes = 16 * kNibBytes; cur.pf_end = cur.pf + nrows * kNibBytes; }
-                else if (lane == 1)        { cur.pf = a.v_nib + row0 * kNibBytes; cur.pf_bytes = 16 * kNibBytes; cur.pf_end = cur.pf + nrows * kNibBytes; }
-                else if (QJL && lane == 2) { cur.pf = a.k_qjl + row0 * kQjlBytes; cur.pf_bytes = 16 * kQjlBytes; cur.pf_end = cur.pf + nrows * kQjlBytes; }
-                else if (QJL && lane == 3) { cur.pf = reinterpret_cast<const uint8_t*>(a.k_norms + row0); cur.pf_bytes = 16 * 4; cur.pf_end = cur.pf + nrows * 4; }
-            }
-            if (cur.pf_bytes) {
-                // the first blocks in one request, then one block per step
-                cur.pf = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(cur.pf) & ~(uintptr_t)15);
-                const uint32_t room = (uint32_t)(cur.pf_end - cur.pf) & ~15u;
-                // stream s is refreshed at block steps j = s (mod 4): start it s blocks further ahead
-                const uint32_t want = (kPrefetchBlocks + lane) * cur.pf_bytes + 16u;
-                const uint32_t n = room < want ? room : want;
-                if (n) prefetch_l2_bulk(cur.pf, n);
-                cur.pf += (kPrefetchBlocks + lane) * cur.pf_bytes;
-            }
-            KeyBlock blk_a, blk_b;
-            if (nfull > 0) load_full_block<QJL>(blk_a, cur);
-            int j = 0;
-            for (; j + 1 < nfull; j += 2) {            // blocks j (in blk_a) and j+1 are full
-                load_full_block<QJL>(blk_b, cur);
-                prefetch_step(cur, j, lane);
-                process_key_block<QJL, false>(blk_a, st, qB, gB, post0, post1, lut_lane, sgn_lane, 16, kl);
-                if (j + 2 < nfull) load_full_block<QJL>(blk_a, cur);
-                prefetch_step(cur, j + 1, lane);
-                process_key_block<QJL, false>(blk_b, st, qB, gB, post0, post1, lut_lane, sgn_lane, 16, kl);
-            }
-            if (j < nfull)                              // odd count: the last full block is already in blk_a
-                process_key_block<QJL, false>(blk_a, st, qB, gB, post0, post1, lut_lane, sgn_lane, 16, kl);
-            if (rem) {                                   // partial block: clamped loads, masked scores
-                load_tail_block<QJL>(blk_b, cur, rem, kl, t);
-                process_key_block<QJL, true>(blk_b, st, qB, gB, post0, post1, lut_lane, sgn_lane, rem, kl);
-            }
-        }
-
-        // ---- epilogue ----------------------------------------------------------------------
-#pragma unroll
-        for (int m = 4; m <= 16; m <<= 1) {
-            st.l0 += __shfl_xor_sync(kFullMask, st.l0, m);
-            st.l1 += __shfl_xor_sync(kFullMask, st.l1, m);
-        }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int c = 2 * t + j;
-            if (c >= ncols) continue;
-            const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + c / a.T) * a.T + (c % a.T);
-            const float l = j ? st.l1 : st.l0;
-            const float m = j ? st.m1 : st.m0;
-            float* dst;
-            float mul;
-            if (a.n_splits == 1) {
-                dst = a.out + qrow * kHeadDim + 16 * g;
-                mul = l > 0.f ? 1.f / l : 0.f;
-            } else {
-                float* w = a.ws + (qrow * a.n_splits + split) * kWsStride;
-                dst = w + 16 * g;
-                mul = 1.f;
-                if (g == 0) { w[128] = m * 0.6931471805599453f; w[129] = l; }   // max back in natural-log units
-            }
-#pragma unroll
-            for (int mp = 0; mp < 4; ++mp) {      // d = 16g + 4mp .. 16g + 4mp + 3  (m-tiles 2mp, 2mp+1)
-                float4 v;
-                v.x = st.O[2 * mp][j] * mul;     v.y = st.O[2 * mp][2 + j] * mul;
-                v.z = st.O[2 * mp + 1][j] * mul; v.w = st.O[2 * mp + 1][2 + j] * mul;
-                *reinterpret_cast<float4*>(dst + 4 * mp) = v;
-            }
-        }
-    }
-}
-
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 static int32_t validate(const AttnArgs& a, size_t ws_bytes) {
@@ -746,51 +232,12 @@ static KernelChoice kernel_choice_from_env() {
     return kAuto;
 }
 
-static bool mma_eligible(const AttnArgs& a) {
-    const int cols = (a.Hq / a.Hkv) * a.T;
-    return cols <= 8 && !a.rotate_q && !a.unrotate_out && a.Hkv <= 65535;
-}
-
-template <int DT>
-static int32_t launch_mma(const AttnArgs& a, cudaStream_t st) {
-    int dev = 0, sms = 148;
-    OMNI_CUDA(cudaGetDevice(&dev));
-    OMNI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    // Persistent CTAs, one per SM.  With one shared codebook a CTA serves every kv head
-    // (grid.y == 1, the head is part of the item index); with per-head codebooks a CTA is
-    // bound to one head because its lookup table is built from that head's centroids.
-    int64_t items, ctas;
-    unsigned gy;
-    if (a.cb_per_head) {
-        items = a.B * a.n_splits;
-        ctas = sms / a.Hkv > 0 ? sms / a.Hkv : 1;
-        gy = (unsigned)a.Hkv;
-    } else {
-        items = a.B * a.n_splits * a.Hkv;
-        ctas = sms;
-        gy = 1;
-    }
-    const int64_t need = (items + kMmaWarps - 1) / kMmaWarps;
-    if (ctas > need) ctas = need;
-    dim3 grid((unsigned)ctas, gy);
-    auto kern = a.with_qjl ? qattn_mma_kernel<DT, true> : qattn_mma_kernel<DT, false>;
-    OMNI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemBytes));
-    kern<<<grid, kMmaWarps * 32, kMmaSmemBytes, st>>>(a, items);
-    return check_cuda(cudaGetLastError(), "qattn_mma_kernel launch");
-}
-
 static int32_t launch(const AttnArgs& a, cudaStream_t st) {
     if (a.B == 0 || a.T == 0) return OMNI_OK;
     const KernelChoice choice = kernel_choice_from_env();
     const bool use_mma = mma_eligible(a) && (choice == kMma || (choice == kAuto && a.S >= 128));
     if (use_mma) {
-        int32_t rc;
-        switch (a.q_dtype) {
-            case OMNI_F32:  rc = launch_mma<OMNI_F32>(a, st); break;
-            case OMNI_BF16: rc = launch_mma<OMNI_BF16>(a, st); break;
-            case OMNI_F16:  rc = launch_mma<OMNI_F16>(a, st); break;
-            default: return set_error(OMNI_ERR_ARG, "qattn: unknown q dtype code %d", a.q_dtype);
-        }
+        const int32_t rc = launch_mma(a, st);
         if (rc != OMNI_OK) return rc;
     } else {
         const int64_t n_work = a.B * a.Hq * a.T * a.n_splits;
@@ -871,12 +318,11 @@ extern "C" int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
                                      int32_t rotate_q, int32_t unrotate_out, int32_t n_splits,
                                      void* workspace, size_t workspace_bytes, float* out,
                                      int32_t* status_word, void* stream) {
-    (void)status_word;   // this kernel has no device-side waits
     const DeviceTables* tb = tables_for_current_device();
     if (!tb) return OMNI_ERR_NOT_INIT;
     AttnArgs a{q, q_dtype, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id, seq_lens,
                cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
-               (float*)workspace, out, tb->rows};
+               (float*)workspace, out, tb->rows, status_word};
     int32_t st = validate(a, workspace_bytes);
     if (st != OMNI_OK) return st;
     return launch(a, (cudaStream_t)stream);
@@ -920,7 +366,7 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
                    k_norms ? k_norms + row0 : nullptr, v_nib + row0 * kNibBytes,
                    codebooks, cb_per_head, user_ids ? user_ids + b0 : nullptr, user_id,
                    seq_lens ? seq_lens + b0 : nullptr, cache_slots ? cache_slots + b0 : nullptr,
-                   nb, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, 0, 0, 1, nullptr, out_stage + qoff, tb->rows};
+                   nb, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, 0, 0, 1, nullptr, out_stage + qoff, tb->rows, nullptr};
         int32_t stc = validate(a, 0);
         if (stc == OMNI_OK) stc = launch(a, st);
         if (stc != OMNI_OK) { cudaStreamSynchronize(g_hs[dev].s[0]); cudaStreamSynchronize(g_hs[dev].s[1]); return stc; }
@@ -953,7 +399,7 @@ extern "C" int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
     if (st != OMNI_OK) return st;
     AttnArgs a{q, q_dtype, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id, seq_lens,
                cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
-               arr.scratch, out, arr.rows};
+               arr.scratch, out, arr.rows, nullptr};
     st = validate(a, kStaticScratchBytes);
     if (st != OMNI_OK) return st;
     return launch(a, (cudaStream_t)stream);

@@ -1,0 +1,36 @@
+// Declarations shared by the decode-attention translation units.
+#pragma once
+#include "common.cuh"
+
+namespace omni {
+
+struct AttnArgs {
+    const void* q; int q_dtype;
+    const uint8_t* k_nib; const uint8_t* k_qjl; const float* k_norms; const uint8_t* v_nib;
+    const float* codebooks; int cb_per_head;
+    const int32_t* user_ids; int32_t user_id;
+    const int32_t* seq_lens; const int32_t* cache_slots;
+    int64_t B; int Hq, Hkv, T; int64_t S; int64_t ks_b, ks_h;
+    float scale; int with_qjl, rotate_q, unrotate_out; int n_splits;
+    float* ws; float* out; const uint32_t* g_rows;
+    int32_t* status;           // device word set non-zero when a bounded wait expires (may be null)
+};
+
+constexpr int kWsStride = 132;     // floats per split-K partial: 128 accumulators, max, sum, 2 pad
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, m));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(kFullMask, v, m);
+    return v;
+}
+
+// Tensor-core kernel (qattn_mma.cu): shapes it covers, and its launcher.
+bool mma_eligible(const AttnArgs& a);
+int32_t launch_mma(const AttnArgs& a, cudaStream_t st);
+
+}  // namespace omni

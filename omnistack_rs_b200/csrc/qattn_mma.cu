@@ -1,0 +1,750 @@
+// Tensor-core decode attention over the packed INT4 + QJL cache (sm_100a).
+//
+// One warp owns one (user, kv head, key split) and all query columns of that kv head (a
+// column = one (query head of the group, query token); at most 8).  Keys are taken 16 at a
+// time and everything is computed transposed so that the key axis is the MMA "M":
+//     S^T[key, col]  = sum_d  K^[key, d] * q[col, d]                 (8 MMAs, A = dequantised K)
+//                    + norm[key] * sum_i s_i[key] * (q.g_i)[col]      (4 MMAs, A = +-1)
+//     O^T[d,  col]  += sum_key V^[key, d] * P[key, col]               (8 MMAs, A = dequantised V^T)
+// (mma.sync m16n8k16, fp16 operands, fp32 accumulate).
+//
+// Data movement.  The 64-byte nibble rows of K and V are brought in by TMA
+// (cp.async.bulk.tensor.2d, one 16-row box per array and block, 64-byte swizzle) into a
+// private ring of stages per warp, completion tracked by one mbarrier per stage; the lane
+// that issues a copy is lane 0 of the warp that consumes it, so no cross-warp handshake
+// exists.  Sign bytes and norms (12 of the 140 bytes per key) are read with plain loads one
+// block ahead.  Every wait on an mbarrier is bounded; when the bound is hit the warp
+// records it in the status word, waits (bounded again) for its other copies and leaves.
+//
+// Dequantisation.  A fragments are built straight from the packed bytes with table lookups
+// in shared memory: a 256-entry table maps a byte to half2(cb[low nibble], cb[high nibble]),
+// replicated per lane so every lookup is bank-conflict free; a second table maps a byte made
+// of two 4-bit sign groups to the four half2 of +-1.0 of one MMA.  Both live in one 64 KiB
+// region placed on a 64 KiB boundary of the shared window, so that a single PRMT (byte ->
+// address bits 8..15) forms the complete address.  The contraction index of each MMA is a
+// permutation of d (or of the projections) chosen so that each thread reads 16 contiguous
+// bytes of a key row; for V the two nibbles of a pair come from two different keys and the
+// index byte is formed with one shift and one LOP3 per four lookups.  The rows of the score
+// tile are a permutation rho of the 16 keys chosen so that (a) the transposed softmax
+// weights come out of MOVMATRIX in the order the V fragments need and (b) every shared-memory
+// read of a stage is conflict free under the 64-byte swizzle.
+#include "qattn.cuh"
+#include <cuda.h>
+#include <mutex>
+
+namespace omni {
+
+#ifndef OMNI_MMA_WARPS
+#define OMNI_MMA_WARPS 12
+#endif
+#ifndef OMNI_MMA_STAGES
+#define OMNI_MMA_STAGES 2
+#endif
+constexpr int kMmaWarps = OMNI_MMA_WARPS;
+constexpr int kStages = OMNI_MMA_STAGES;                 // per-warp ring of stages
+constexpr int kStageKeys = 32;                           // keys per stage: two 16-key MMA blocks
+constexpr int kLutSpan = 65536;                          // 256 entries x 256 B
+constexpr int kStageBytes = 2 * kStageKeys * kNibBytes;  // K rows then V rows of one stage
+constexpr int kWarpScratchBytes = 512 + 8 * 64 * 4;      // one fp32 query row + q.g for 8 columns
+// Per-warp private block, 1 KiB aligned (the swizzle pattern of a stage repeats every 512 bytes):
+// [kStages stages][scratch][kStages mbarriers][pad]
+constexpr int kWarpBlockBytes = ((kStages * kStageBytes + kWarpScratchBytes + 8 * kStages + 1023) / 1024) * 1024;
+// Dynamic shared memory: the whole SM.  The tables take the 64 KiB that start at the first 64 KiB
+// boundary of the shared window; the per-warp blocks fill the space in front of and behind them.
+constexpr int kMmaSmemBytes = 227 * 1024;
+static_assert(kMmaWarps * kWarpBlockBytes + kLutSpan + kWarpBlockBytes <= kMmaSmemBytes,
+              "per-warp blocks do not fit beside the tables for every placement of the 64 KiB boundary");
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr uint32_t kWaitLimit = 1u << 20;                // try_wait attempts before a wait is declared expired
+
+// ---- PTX wrappers ----------------------------------------------------------------------
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// first MMA of a chain: D = A*B with a zero addend (no accumulator registers to clear)
+__device__ __forceinline__ void mma_f16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream8(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream2(const void* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];\n" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ldg_stream_f32(const void* p) {
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];\n" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds8(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+// Bulk L2 prefetch (issued by the TMA unit): `bytes` (multiple of 16) from a 16-byte aligned address.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" :: "l"(p), "r"(bytes) : "memory");
+}
+// centroid-table lookup: byte WHICH of w selects the entry; lut_lane has zero bits 8..15
+template <int WHICH>
+__device__ __forceinline__ uint32_t lut_at(uint32_t lut_lane, uint32_t w) {
+    const uint32_t addr = __byte_perm(w, lut_lane, 0x7604 | (WHICH << 4));
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));   // read-only table: free to be scheduled early
+    return v;
+}
+// sign-table lookup: byte WHICH of s = (sign nibble of key row g) | (sign nibble of key row g+8) << 4
+// selects the four A registers of one MMA; sgn_lane has zero bits 8..15
+template <int WHICH>
+__device__ __forceinline__ uint4 sgn_at(uint32_t sgn_lane, uint32_t s) {
+    const uint32_t addr = __byte_perm(s, sgn_lane, 0x7604 | (WHICH << 4));
+    uint4 v;
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__host__ __device__ constexpr uint32_t sign_half2(uint32_t bit0, uint32_t bit1) {
+    return 0x3C003C00u ^ (bit0 ? 0u : 0x8000u) ^ (bit1 ? 0u : 0x80000000u);
+}
+
+// ---- QJL correction operands --------------------------------------------------------------
+// Two ways to feed the 64 sign bits of a key to the tensor cores (OMNI_SIGN_INT8 selects):
+//   0: fp16 MMA, A = +-1.0 read from the sign table in shared memory (4 LDS.128 per block);
+//   1: int8 MMA, A = -bit built in registers (multiply spreads 4 bits to the 4 byte MSBs, PRMT
+//      replicates them), B = q.g quantised to int8 per column; no shared-memory traffic.
+#ifndef OMNI_SIGN_INT8
+#define OMNI_SIGN_INT8 0
+#endif
+struct SignB {
+#if OMNI_SIGN_INT8
+    uint32_t z[4];          // int8 x4: q.g of column g, projections 16t .. 16t+15
+    int zq[4];              // accumulator seed (sum of z)/2 for columns 2t, 2t+1, 2t, 2t+1
+    float cs0, cs1;         // -2 * quantisation step of columns 2t, 2t+1
+#else
+    uint32_t g[4][2];       // half2: q.g of column g, projections 16t + 4kk .. +3
+#endif
+};
+__device__ __forceinline__ void imma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1, const int (&c)[4]) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+// four int8 (0 or -1) from the 4 bits of `nib` that sit at bit positions LOW..LOW+3 (LOW = 0 or 4)
+template <int LOW>
+__device__ __forceinline__ uint32_t neg_bits_s8(uint32_t s) {
+    const uint32_t spread = (s & (0xFu << LOW)) * (LOW == 0 ? 0x10204080u : 0x01020408u);   // bit j -> MSB of byte j
+    return __byte_perm(spread, 0, 0xBA98);                                                  // replicate each MSB
+}
+
+// ---- mbarrier / TMA ---------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false when kWaitLimit attempts did not see the phase complete
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, int32_t row, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 :: "r"(dst), "l"(map), "r"(0), "r"(row), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+}
+
+// ---- per-thread view of one 16-key block ---------------------------------------------------
+// Score-tile row r of the MMA holds key rho(r) of the block: rho = {0,3,1,2,4,7,5,6} for r < 8 and
+// rho(r) = rho(r-8) + 8 above.  Thread (g, t) (g = lane/4, t = lane%4) therefore reads the K rows
+// rho(g), rho(g)+8 and, after the transposition of the weights, the V rows rho(2t), rho(2t+1) and
+// those plus 8.
+__device__ __forceinline__ int rho8(int r) { return (0x65742130 >> (4 * r)) & 7; }
+
+struct KeyBlock {           // packed bytes of one 16-key block as this thread needs them
+    uint4 ka, kb;           // K nibbles: keys rho(g) and rho(g)+8, bytes 16t..16t+15
+    uint2 v0, v1, v2, v3;   // V nibbles: keys rho(2t), rho(2t+1), rho(2t)+8, rho(2t+1)+8, bytes 8g..8g+7
+    uint32_t sa, sb;        // K sign bits: keys rho(g), rho(g)+8, bits 16t..16t+15
+    float na, nb;           // K residual norms: keys rho(g), rho(g)+8
+};
+
+// Sign bytes and norms of one block (plain loads, kept one block ahead of their use).
+struct AuxRegs { uint32_t sa, sb; float na, nb; };
+__device__ __forceinline__ void load_aux(AuxRegs& x, const uint8_t* ps, const float* pn) {
+    x.sa = ldg_stream2(ps);
+    x.sb = ldg_stream2(ps + 8 * kQjlBytes);
+    x.na = ldg_stream_f32(pn);
+    x.nb = ldg_stream_f32(pn + 8);
+}
+
+// Partial last block, read with plain loads: rows past the end are clamped to the last valid key
+// (their scores are masked).  row0 = first row of the block in the packed arrays.
+template <bool QJL>
+__device__ __forceinline__ void load_tail_block(KeyBlock& kb, const AttnArgs& a, int64_t row0, int nvalid,
+                                                int kr, int va, int vb, int g, int t) {
+    const int last = nvalid - 1;
+    const int64_t rk = row0 + min(kr, last), rk8 = row0 + min(kr + 8, last);
+    kb.ka = ldg_stream16(a.k_nib + rk * kNibBytes + 16 * t);
+    kb.kb = ldg_stream16(a.k_nib + rk8 * kNibBytes + 16 * t);
+    kb.v0 = ldg_stream8(a.v_nib + (row0 + min(va, last)) * kNibBytes + 8 * g);
+    kb.v1 = ldg_stream8(a.v_nib + (row0 + min(vb, last)) * kNibBytes + 8 * g);
+    kb.v2 = ldg_stream8(a.v_nib + (row0 + min(va + 8, last)) * kNibBytes + 8 * g);
+    kb.v3 = ldg_stream8(a.v_nib + (row0 + min(vb + 8, last)) * kNibBytes + 8 * g);
+    if (QJL) {
+        kb.sa = ldg_stream2(a.k_qjl + rk * kQjlBytes + 2 * t);
+        kb.sb = ldg_stream2(a.k_qjl + rk8 * kQjlBytes + 2 * t);
+        kb.na = ldg_stream_f32(a.k_norms + rk);
+        kb.nb = ldg_stream_f32(a.k_norms + rk8);
+    }
+}
+
+struct WarpState {
+    float O[8][4];          // O^T accumulators: [m-tile][c-fragment]
+    float m0, m1, l0, l1;   // reference maximum (log2 units) and partial sums for columns 2t, 2t+1
+};
+
+constexpr float kLazyMaxSlack = 6.f;   // log2 units a score may exceed the reference maximum before it is raised
+
+
+template <bool QJL, bool TAIL>
+__device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState& st, const uint32_t (&qB)[8][2],
+                                                  const SignB& sg, float post0, float post1,
+                                                  uint32_t lut_lane, uint32_t sgn_lane, int nvalid, int kl) {
+    // two independent accumulator chains per product so consecutive MMAs do not wait on each other
+    float cd[4], ce[4];
+    {
+        const uint32_t wa[4] = {kb.ka.x, kb.ka.y, kb.ka.z, kb.ka.w};
+        const uint32_t wb[4] = {kb.kb.x, kb.kb.y, kb.kb.z, kb.kb.w};
+        // k-step 2w: bytes 0,1 of word w; k-step 2w+1: bytes 2,3
+        mma_f16_first(cd, lut_at<0>(lut_lane, wa[0]), lut_at<0>(lut_lane, wb[0]),
+                          lut_at<1>(lut_lane, wa[0]), lut_at<1>(lut_lane, wb[0]), qB[0][0], qB[0][1]);
+        mma_f16_first(ce, lut_at<2>(lut_lane, wa[0]), lut_at<2>(lut_lane, wb[0]),
+                          lut_at<3>(lut_lane, wa[0]), lut_at<3>(lut_lane, wb[0]), qB[1][0], qB[1][1]);
+#pragma unroll
+        for (int w = 1; w < 4; ++w) {
+            mma_f16(cd, lut_at<0>(lut_lane, wa[w]), lut_at<0>(lut_lane, wb[w]),
+                        lut_at<1>(lut_lane, wa[w]), lut_at<1>(lut_lane, wb[w]), qB[2 * w][0], qB[2 * w][1]);
+            mma_f16(ce, lut_at<2>(lut_lane, wa[w]), lut_at<2>(lut_lane, wb[w]),
+                        lut_at<3>(lut_lane, wa[w]), lut_at<3>(lut_lane, wb[w]), qB[2 * w + 1][0], qB[2 * w + 1][1]);
+        }
+    }
+    float s00, s01, s80, s81;           // scores of keys rho(g) / rho(g)+8 for columns 2t / 2t+1, log2 units
+    if (QJL) {
+#if OMNI_SIGN_INT8
+        // sum_i s_i z_i = -2 * (sum_i (-bit_i) z_i + Z/2): the seed Z/2 rides in as the MMA addend
+        const uint32_t sa8 = kb.sa >> 8, sb8 = kb.sb >> 8;
+        int d0[4], d1[4];
+        imma_s8(d0, neg_bits_s8<0>(kb.sa), neg_bits_s8<0>(kb.sb), neg_bits_s8<4>(kb.sa), neg_bits_s8<4>(kb.sb),
+                sg.z[0], sg.z[1], sg.zq);
+        imma_s8(d1, neg_bits_s8<0>(sa8), neg_bits_s8<0>(sb8), neg_bits_s8<4>(sa8), neg_bits_s8<4>(sb8),
+                sg.z[2], sg.z[3], d0);
+        s00 = post0 * fmaf(kb.na * sg.cs0, (float)d1[0], cd[0] + ce[0]);
+        s01 = post1 * fmaf(kb.na * sg.cs1, (float)d1[1], cd[1] + ce[1]);
+        s80 = post0 * fmaf(kb.nb * sg.cs0, (float)d1[2], cd[2] + ce[2]);
+        s81 = post1 * fmaf(kb.nb * sg.cs1, (float)d1[3], cd[3] + ce[3]);
+#else
+        float cq[4], cr[4];
+        // sign groups of the two key rows side by side: byte 0/1 of sx -> bits 0-3 / 8-11, of sy -> bits 4-7 / 12-15
+        const uint32_t sx = (kb.sa & 0x0F0Fu) | ((kb.sb << 4) & 0xF0F0u);
+        const uint32_t sy = ((kb.sa >> 4) & 0x0F0Fu) | (kb.sb & 0xF0F0u);
+        const uint4 q0 = sgn_at<0>(sgn_lane, sx), q1 = sgn_at<0>(sgn_lane, sy);
+        const uint4 q2 = sgn_at<1>(sgn_lane, sx), q3 = sgn_at<1>(sgn_lane, sy);
+        mma_f16_first(cq, q0.x, q0.y, q0.z, q0.w, sg.g[0][0], sg.g[0][1]);
+        mma_f16_first(cr, q1.x, q1.y, q1.z, q1.w, sg.g[1][0], sg.g[1][1]);
+        mma_f16(cq, q2.x, q2.y, q2.z, q2.w, sg.g[2][0], sg.g[2][1]);
+        mma_f16(cr, q3.x, q3.y, q3.z, q3.w, sg.g[3][0], sg.g[3][1]);
+        s00 = post0 * fmaf(kb.na, cq[0] + cr[0], cd[0] + ce[0]);
+        s01 = post1 * fmaf(kb.na, cq[1] + cr[1], cd[1] + ce[1]);
+        s80 = post0 * fmaf(kb.nb, cq[2] + cr[2], cd[2] + ce[2]);
+        s81 = post1 * fmaf(kb.nb, cq[3] + cr[3], cd[3] + ce[3]);
+#endif
+    } else {
+        s00 = post0 * (cd[0] + ce[0]); s01 = post1 * (cd[1] + ce[1]);
+        s80 = post0 * (cd[2] + ce[2]); s81 = post1 * (cd[3] + ce[3]);
+    }
+    if (TAIL) {
+        if (kl >= nvalid) { s00 = -INFINITY; s01 = -INFINITY; }
+        if (kl + 8 >= nvalid) { s80 = -INFINITY; s81 = -INFINITY; }
+    }
+    // Lazy running maximum: the reference point m of a column is raised only when some score
+    // exceeds it by more than kLazyMaxSlack, so the cross-lane reduction and the rescale of the
+    // accumulators run on few blocks; in between, weights are at most 2^kLazyMaxSlack.
+    const bool exceed = (fmaxf(s00, s80) > st.m0 + kLazyMaxSlack) || (fmaxf(s01, s81) > st.m1 + kLazyMaxSlack);
+    if (__any_sync(kFullMask, exceed)) {
+        float mx0 = fmaxf(s00, s80), mx1 = fmaxf(s01, s81);
+#pragma unroll
+        for (int m = 4; m <= 16; m <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(kFullMask, mx0, m));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(kFullMask, mx1, m));
+        }
+        const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
+        const float al0 = ex2_approx(st.m0 - mn0), al1 = ex2_approx(st.m1 - mn1);
+        st.l0 *= al0; st.l1 *= al1;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            st.O[mt][0] *= al0; st.O[mt][1] *= al1; st.O[mt][2] *= al0; st.O[mt][3] *= al1;
+        }
+        st.m0 = mn0; st.m1 = mn1;
+    }
+    const float p00 = ex2_approx(s00 - st.m0), p01 = ex2_approx(s01 - st.m1);
+    const float p80 = ex2_approx(s80 - st.m0), p81 = ex2_approx(s81 - st.m1);
+    st.l0 += p00 + p80;
+    st.l1 += p01 + p81;
+    // P^T as the B operand: transpose the two 8x8 (key x column) blocks across the warp
+    const uint32_t pb0 = movmatrix_trans(pack_half2(p00, p01));
+    const uint32_t pb1 = movmatrix_trans(pack_half2(p80, p81));
+    // V: index byte = nibble of key A | nibble of key B << 4
+    {
+        const uint32_t A[2] = {kb.v0.x, kb.v0.y}, B[2] = {kb.v1.x, kb.v1.y};
+        const uint32_t C[2] = {kb.v2.x, kb.v2.y}, D[2] = {kb.v3.x, kb.v3.y};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t x01 = (A[h] & 0x0F0F0F0Fu) | ((B[h] << 4) & 0xF0F0F0F0u);
+            const uint32_t y01 = ((A[h] >> 4) & 0x0F0F0F0Fu) | (B[h] & 0xF0F0F0F0u);
+            const uint32_t x23 = (C[h] & 0x0F0F0F0Fu) | ((D[h] << 4) & 0xF0F0F0F0u);
+            const uint32_t y23 = ((C[h] >> 4) & 0x0F0F0F0Fu) | (D[h] & 0xF0F0F0F0u);
+            mma_f16(st.O[4 * h + 0], lut_at<0>(lut_lane, x01), lut_at<0>(lut_lane, y01),
+                                     lut_at<0>(lut_lane, x23), lut_at<0>(lut_lane, y23), pb0, pb1);
+            mma_f16(st.O[4 * h + 1], lut_at<1>(lut_lane, x01), lut_at<1>(lut_lane, y01),
+                                     lut_at<1>(lut_lane, x23), lut_at<1>(lut_lane, y23), pb0, pb1);
+            mma_f16(st.O[4 * h + 2], lut_at<2>(lut_lane, x01), lut_at<2>(lut_lane, y01),
+                                     lut_at<2>(lut_lane, x23), lut_at<2>(lut_lane, y23), pb0, pb1);
+            mma_f16(st.O[4 * h + 3], lut_at<3>(lut_lane, x01), lut_at<3>(lut_lane, y01),
+                                     lut_at<3>(lut_lane, x23), lut_at<3>(lut_lane, y23), pb0, pb1);
+        }
+    }
+}
+
+
+// Per-warp ring of TMA stages: each holds kStageKeys rows of K nibbles followed by as many of V.
+// The stage filled next and the stage consumed next advance round-robin; `*_phase` is the parity of
+// the mbarrier phase that the fill completes / the consumer waits for.
+struct Ring {
+    uint32_t stage0;        // shared address of stage 0 (stages are contiguous, kStageBytes apart)
+    uint32_t bar0;          // shared address of mbarrier 0 (8 bytes apart)
+    uint32_t fill, use;     // stage indices
+    uint32_t use_phase;     // parity to wait for at `use`
+    uint32_t in_flight;     // fills issued and not yet consumed
+};
+
+__device__ __forceinline__ void ring_issue(Ring& r, const CUtensorMap* mk, const CUtensorMap* mv, int32_t row, int lane) {
+    if (lane == 0) {
+        const uint32_t bar = r.bar0 + 8 * r.fill, dst = r.stage0 + r.fill * kStageBytes;
+        fence_proxy_async();                     // earlier reads of this stage are ordered before the refill
+        mbar_expect_tx(bar, kStageBytes);
+        tma_load_rows(dst, mk, row, bar);
+        tma_load_rows(dst + kStageKeys * kNibBytes, mv, row, bar);
+    }
+    r.fill = (r.fill + 1 == kStages) ? 0u : r.fill + 1;
+    ++r.in_flight;
+}
+__device__ __forceinline__ void ring_consumed(Ring& r) {
+    if (r.use + 1 == kStages) { r.use = 0; r.use_phase ^= 1u; } else { ++r.use; }
+    --r.in_flight;
+}
+
+template <int DT, bool QJL>
+__global__ void __launch_bounds__(kMmaWarps * 32, 1)
+qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int kr = rho8(g);                                   // K / score row of this thread (and kr + 8)
+    const int va = rho8(2 * t), vb = rho8(2 * t + 1);         // V rows of this thread (and those + 8)
+    const bool head_in_item = (gridDim.y == 1 && a.Hkv > 1);  // shared codebook: a CTA serves all kv heads
+    const int cb_head = blockIdx.y;
+
+    // ---- shared memory carve-up -------------------------------------------------------------
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t lut_off = (kLutSpan - (smem_base & (kLutSpan - 1))) & (kLutSpan - 1);
+    // warps [0, n_front) live in front of the tables, the others behind them
+    const uint32_t n_front = lut_off / kWarpBlockBytes;
+    const uint32_t my_off = (uint32_t)warp < n_front ? (uint32_t)warp * kWarpBlockBytes
+                                                     : lut_off + kLutSpan + ((uint32_t)warp - n_front) * kWarpBlockBytes;
+    {
+        const float* cb = a.codebooks + (a.cb_per_head ? cb_head * 16 : 0);
+        uint32_t* lut = reinterpret_cast<uint32_t*>(smem + lut_off);
+        for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+            const int byte = i >> 5, ln = i & 31;
+            lut[byte * 64 + ln] = pack_half2(__ldg(cb + (byte & 15)), __ldg(cb + (byte >> 4)));
+        }
+        if (QJL && !OMNI_SIGN_INT8) {   // sign table in the upper half of every 256-byte slot: 8 copies of 16 bytes
+            for (int i = threadIdx.x; i < 256 * 8; i += blockDim.x) {
+                const uint32_t b = i >> 3, na = b & 15, nb = b >> 4;
+                uint4* dst = reinterpret_cast<uint4*>(smem + lut_off + b * 256 + 128) + (i & 7);
+                *dst = make_uint4(sign_half2(na & 1, na & 2), sign_half2(nb & 1, nb & 2),
+                                  sign_half2(na & 4, na & 8), sign_half2(nb & 4, nb & 8));
+            }
+        }
+    }
+    const uint32_t lut_lane = smem_base + lut_off + 4 * lane;                  // bits 8..15 are zero
+    const uint32_t sgn_lane = smem_base + lut_off + 128 + 16 * (lane & 7);    // likewise
+    float* qf = reinterpret_cast<float*>(smem + my_off + kStages * kStageBytes);
+    float* qg_s = qf + 128;                                                    // [8][64]
+    Ring ring;
+    ring.stage0 = smem_base + my_off;
+    ring.bar0 = smem_base + my_off + kStages * kStageBytes + kWarpScratchBytes;
+    ring.fill = 0; ring.use = 0; ring.use_phase = 0; ring.in_flight = 0;
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(ring.bar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    // swizzled offsets inside a stage (64-byte swizzle: 16-byte chunk index ^= (row >> 1) & 3)
+    const uint32_t off_k = kr * kNibBytes + ((t ^ ((kr >> 1) & 3)) << 4);               // row kr + 8: + 512
+    const uint32_t off_va = kStageKeys * kNibBytes + va * kNibBytes + (((g >> 1) ^ ((va >> 1) & 3)) << 4) + 8 * (g & 1);
+    const uint32_t off_vb = kStageKeys * kNibBytes + vb * kNibBytes + (((g >> 1) ^ ((vb >> 1) & 3)) << 4) + 8 * (g & 1);
+
+    const int Gq = a.Hq / a.Hkv;
+    const int ncols = Gq * a.T;
+    const float qs = a.scale * kLog2e;
+    bool alive = true;
+
+    for (int64_t item = (int64_t)blockIdx.x * kMmaWarps + warp; alive && item < n_items;
+         item += (int64_t)gridDim.x * kMmaWarps) {
+        int64_t rest = item;
+        int hkv = cb_head;
+        if (head_in_item) { hkv = (int)(rest % a.Hkv); rest /= a.Hkv; }
+        const int split = (int)(rest % a.n_splits);
+        const int64_t b = rest / a.n_splits;
+
+        // ---- key range of this split; start the first copies before the prologue ------------------
+        int64_t len = a.seq_lens ? (int64_t)a.seq_lens[b] : a.S;
+        len = len < 0 ? 0 : (len > a.S ? a.S : len);
+        int64_t per = (len + a.n_splits - 1) / a.n_splits;
+        per = (per + 31) / 32 * 32;
+        const int64_t s0 = (int64_t)split * per;
+        const int64_t s1 = (s0 + per < len) ? s0 + per : len;
+        const int64_t slot = a.cache_slots ? (int64_t)a.cache_slots[b] : b;
+        const int64_t row0 = slot * a.ks_b + (int64_t)hkv * a.ks_h + s0;
+        const int nkeys = s1 > s0 ? (int)(s1 - s0) : 0;
+        const int nstage = nkeys / kStageKeys;                 // full stages; the rest (< 32 keys) uses plain loads
+        {
+            const int prime = nstage < kStages ? nstage : kStages;
+            for (int j = 0; j < prime; ++j) ring_issue(ring, &map_k, &map_v, (int32_t)(row0 + kStageKeys * j), lane);
+        }
+        const uint8_t* ps = a.k_qjl + (row0 + kr) * kQjlBytes + 2 * t;      // sign bytes / norm of row kr, block 0
+        const float* pn = a.k_norms + row0 + kr;
+        AuxRegs aux_a, aux_b;                                   // sign bytes / norms of the two blocks of the next stage
+        if (QJL && nstage > 0) {
+            if (lane == 2) prefetch_l2_bulk(reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(a.k_qjl + row0 * kQjlBytes) & ~(uintptr_t)15),
+                                            (uint32_t)(nstage * kStageKeys * kQjlBytes) & ~15u);
+            if (lane == 3) prefetch_l2_bulk(reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(a.k_norms + row0) & ~(uintptr_t)15),
+                                            (uint32_t)(nstage * kStageKeys * 4) & ~15u);
+            load_aux(aux_a, ps, pn);
+            load_aux(aux_b, ps + 16 * kQjlBytes, pn + 16);
+        }
+
+        // ---- prologue: B operands (scaled queries, q.g projections) --------------------------------
+        uint32_t qB[8][2];
+        SignB sg;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) { qB[kk][0] = 0u; qB[kk][1] = 0u; }
+#if OMNI_SIGN_INT8
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) { sg.z[kk] = 0u; sg.zq[kk] = 0; }
+        sg.cs0 = 0.f; sg.cs1 = 0.f;
+#else
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) { sg.g[kk][0] = 0u; sg.g[kk][1] = 0u; }
+#endif
+        float post0 = 1.f, post1 = 1.f;
+        uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0;
+        if (QJL) {
+            const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
+            const uint4* grow = reinterpret_cast<const uint4*>(a.g_rows) + (size_t)seed_of(uid, hkv) * kQjlDim;
+            g0 = __ldg(grow + lane); g1 = __ldg(grow + lane + 32);
+        }
+        for (int c = 0; c < ncols; ++c) {
+            const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + c / a.T) * a.T + (c % a.T);
+            float qv[4];
+            Elem<DT>::load4(a.q, qrow * kHeadDim + 4 * lane, qv);
+            const float mx = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3])))) * fabsf(qs);
+            // keep the fp16 operands below 2^10 in magnitude; the power of two is re-applied to the scores
+            float post = 1.f;
+            if (mx > 1024.f) post = exp2f(ceilf(log2f(mx * (1.f / 1024.f))));
+            const float f = qs / post;
+            __syncwarp();
+            *reinterpret_cast<float4*>(qf + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
+            __syncwarp();
+            if (QJL) {
+                const uint32_t w0[4] = {g0.x, g0.y, g0.z, g0.w}, w1[4] = {g1.x, g1.y, g1.z, g1.w};
+                float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+#pragma unroll 8
+                    for (int j = 0; j < 32; ++j) {
+                        const float qd = qf[w * 32 + j];
+                        acc0 += ((w0[w] >> j) & 1u) ? qd : -qd;
+                        acc1 += ((w1[w] >> j) & 1u) ? qd : -qd;
+                    }
+                }
+                const float q0 = acc0 * (kQjlCoef * f), q1 = acc1 * (kQjlCoef * f);
+#if OMNI_SIGN_INT8
+                // quantise the 64 projections of this column to int8 with one step; keep their sum even
+                const float amax = warp_max(fmaxf(fabsf(q0), fabsf(q1)));
+                const float step = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
+                int z0 = __float2int_rn(q0 / step), z1 = __float2int_rn(q1 / step);
+                int zsum = z0 + z1;
+#pragma unroll
+                for (int m = 16; m >= 1; m >>= 1) zsum += __shfl_xor_sync(kFullMask, zsum, m);
+                if (zsum & 1) {                                   // warp-uniform: zsum and lane 0's value
+                    const int fix = __shfl_sync(kFullMask, z0, 0) < 127 ? 1 : -1;
+                    if (lane == 0) z0 += fix;
+                    zsum += fix;
+                }
+                int8_t* qz = reinterpret_cast<int8_t*>(qg_s);
+                qz[c * 64 + lane] = (int8_t)z0;
+                qz[c * 64 + lane + 32] = (int8_t)z1;
+                if (c == 2 * t)     { sg.zq[0] = zsum / 2; sg.zq[2] = zsum / 2; sg.cs0 = -2.f * step; }
+                if (c == 2 * t + 1) { sg.zq[1] = zsum / 2; sg.zq[3] = zsum / 2; sg.cs1 = -2.f * step; }
+#else
+                qg_s[c * 64 + lane] = q0;
+                qg_s[c * 64 + lane + 32] = q1;
+#endif
+            }
+            if (g == c) {
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const float4 v = *reinterpret_cast<const float4*>(qf + 32 * t + 4 * kk);
+                    qB[kk][0] = pack_half2(v.x * f, v.y * f);
+                    qB[kk][1] = pack_half2(v.z * f, v.w * f);
+                }
+            }
+            if (c == 2 * t) post0 = post;
+            if (c == 2 * t + 1) post1 = post;
+        }
+        __syncwarp();
+        if (QJL && g < ncols) {
+#if OMNI_SIGN_INT8
+            const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const int8_t*>(qg_s) + g * 64 + 16 * t);
+            sg.z[0] = v.x; sg.z[1] = v.y; sg.z[2] = v.z; sg.z[3] = v.w;
+#else
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const float4 v = *reinterpret_cast<const float4*>(qg_s + g * 64 + 16 * t + 4 * kk);
+                sg.g[kk][0] = pack_half2(v.x, v.y);
+                sg.g[kk][1] = pack_half2(v.z, v.w);
+            }
+#endif
+        }
+
+        WarpState st;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) { st.O[mt][0] = 0.f; st.O[mt][1] = 0.f; st.O[mt][2] = 0.f; st.O[mt][3] = 0.f; }
+        st.m0 = -INFINITY; st.m1 = -INFINITY; st.l0 = 0.f; st.l1 = 0.f;
+
+        // ---- full stages: wait, pull the bytes of a 16-key block into registers, process; refill -----
+        KeyBlock kb;
+        for (int j = 0; j < nstage; ++j) {
+            if (!mbar_wait_bounded(ring.bar0 + 8 * ring.use, ring.use_phase)) { alive = false; break; }
+            const uint32_t base = ring.stage0 + ring.use * kStageBytes;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {                       // rows 0-15, then rows 16-31 of the stage
+                const uint32_t bh = base + h * 16 * kNibBytes;
+                kb.ka = lds16(bh + off_k);
+                kb.kb = lds16(bh + off_k + 8 * kNibBytes);
+                kb.v0 = lds8(bh + off_va);
+                kb.v1 = lds8(bh + off_vb);
+                kb.v2 = lds8(bh + off_va + 8 * kNibBytes);
+                kb.v3 = lds8(bh + off_vb + 8 * kNibBytes);
+                if (QJL) {
+                    const AuxRegs& x = h ? aux_b : aux_a;
+                    kb.sa = x.sa; kb.sb = x.sb; kb.na = x.na; kb.nb = x.nb;
+                }
+                if (h == 1 && QJL && j + 1 < nstage) {          // both halves' aux are consumed: fetch the next stage's
+                    ps += kStageKeys * kQjlBytes; pn += kStageKeys;
+                    load_aux(aux_a, ps, pn);
+                    load_aux(aux_b, ps + 16 * kQjlBytes, pn + 16);
+                }
+                process_key_block<QJL, false>(kb, st, qB, sg, post0, post1, lut_lane, sgn_lane, 16, kr);
+            }
+            // every lane has consumed its bytes of the stage: it can be refilled
+            ring_consumed(ring);
+            __syncwarp();
+            if (j + kStages < nstage) ring_issue(ring, &map_k, &map_v, (int32_t)(row0 + kStageKeys * (j + kStages)), lane);
+        }
+        if (!alive) break;
+        for (int k0 = nstage * kStageKeys; k0 < nkeys; k0 += 16) {     // up to two blocks with plain clamped loads
+            const int nvalid = nkeys - k0 < 16 ? nkeys - k0 : 16;
+            load_tail_block<QJL>(kb, a, row0 + k0, nvalid, kr, va, vb, g, t);
+            process_key_block<QJL, true>(kb, st, qB, sg, post0, post1, lut_lane, sgn_lane, nvalid, kr);
+        }
+
+        // ---- epilogue ----------------------------------------------------------------------
+#pragma unroll
+        for (int m = 4; m <= 16; m <<= 1) {
+            st.l0 += __shfl_xor_sync(kFullMask, st.l0, m);
+            st.l1 += __shfl_xor_sync(kFullMask, st.l1, m);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int c = 2 * t + j;
+            if (c >= ncols) continue;
+            const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + c / a.T) * a.T + (c % a.T);
+            const float l = j ? st.l1 : st.l0;
+            const float m = j ? st.m1 : st.m0;
+            float* dst;
+            float mul;
+            if (a.n_splits == 1) {
+                dst = a.out + qrow * kHeadDim + 16 * g;
+                mul = l > 0.f ? 1.f / l : 0.f;
+            } else {
+                float* w = a.ws + (qrow * a.n_splits + split) * kWsStride;
+                dst = w + 16 * g;
+                mul = 1.f;
+                if (g == 0) { w[128] = m * 0.6931471805599453f; w[129] = l; }   // max back in natural-log units
+            }
+#pragma unroll
+            for (int mp = 0; mp < 4; ++mp) {      // d = 16g + 4mp .. 16g + 4mp + 3  (m-tiles 2mp, 2mp+1)
+                float4 v;
+                v.x = st.O[2 * mp][j] * mul;     v.y = st.O[2 * mp][2 + j] * mul;
+                v.z = st.O[2 * mp + 1][j] * mul; v.w = st.O[2 * mp + 1][2 + j] * mul;
+                *reinterpret_cast<float4*>(dst + 4 * mp) = v;
+            }
+        }
+    }
+
+    if (!alive) {
+        // A wait expired.  Report it, then give the copies still in flight a bounded chance to land
+        // before this warp's shared memory is handed back.
+        if (lane == 0 && a.status) atomicExch(a.status, OMNI_ERR_DEVICE_WAIT);
+        while (ring.in_flight) {
+            mbar_wait_bounded(ring.bar0 + 8 * ring.use, ring.use_phase);
+            ring_consumed(ring);
+        }
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static std::mutex mu;
+    static EncodeTiledFn fn = nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D view [rows][64 bytes] of a nibble array with a kStageKeys-row box and the 64-byte swizzle.  The row
+// extent is the largest a 32-bit row coordinate can address: only full kStageKeys-row boxes that lie inside
+// the caller's arrays are ever requested, so nothing depends on out-of-bounds clipping.
+static int32_t make_nibble_map(CUtensorMap* map, const uint8_t* base) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    OMNI_REQUIRE(fn != nullptr, OMNI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)kNibBytes, (cuuint64_t)0x7fffffffull};
+    const cuuint64_t strides[1] = {(cuuint64_t)kNibBytes};
+    const cuuint32_t box[2] = {(cuuint32_t)kNibBytes, (cuuint32_t)kStageKeys};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    OMNI_REQUIRE(r == CUDA_SUCCESS, OMNI_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return OMNI_OK;
+}
+
+bool mma_eligible(const AttnArgs& a) {
+    const int cols = (a.Hq / a.Hkv) * a.T;
+    return cols <= 8 && !a.rotate_q && !a.unrotate_out && a.Hkv <= 65535;
+}
+
+template <int DT>
+static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
+    int dev = 0, sms = 148;
+    OMNI_CUDA(cudaGetDevice(&dev));
+    OMNI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // Persistent CTAs, one per SM.  With one shared codebook a CTA serves every kv head
+    // (grid.y == 1, the head is part of the item index); with per-head codebooks a CTA is
+    // bound to one head because its lookup table is built from that head's centroids.
+    int64_t items, ctas;
+    unsigned gy;
+    if (a.cb_per_head) {
+        items = a.B * a.n_splits;
+        ctas = sms / a.Hkv > 0 ? sms / a.Hkv : 1;
+        gy = (unsigned)a.Hkv;
+    } else {
+        items = a.B * a.n_splits * a.Hkv;
+        ctas = sms;
+        gy = 1;
+    }
+    const int64_t need = (items + kMmaWarps - 1) / kMmaWarps;
+    if (ctas > need) ctas = need;
+    dim3 grid((unsigned)ctas, gy);
+    CUtensorMap map_k, map_v;
+    int32_t rc = make_nibble_map(&map_k, a.k_nib);
+    if (rc != OMNI_OK) return rc;
+    rc = make_nibble_map(&map_v, a.v_nib);
+    if (rc != OMNI_OK) return rc;
+    auto kern = a.with_qjl ? qattn_mma_kernel<DT, true> : qattn_mma_kernel<DT, false>;
+    OMNI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemBytes));
+    kern<<<grid, kMmaWarps * 32, kMmaSmemBytes, st>>>(a, items, map_k, map_v);
+    return check_cuda(cudaGetLastError(), "qattn_mma_kernel launch");
+}
+
+int32_t launch_mma(const AttnArgs& a, cudaStream_t st) {
+    switch (a.q_dtype) {
+        case OMNI_F32:  return launch_mma_t<OMNI_F32>(a, st);
+        case OMNI_BF16: return launch_mma_t<OMNI_BF16>(a, st);
+        case OMNI_F16:  return launch_mma_t<OMNI_F16>(a, st);
+    }
+    return set_error(OMNI_ERR_ARG, "qattn: unknown q dtype code %d", a.q_dtype);
+}
+
+}  // namespace omni

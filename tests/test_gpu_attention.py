@@ -26,7 +26,9 @@ def kernel_choice(request, monkeypatch):
     lane-per-key kernel or the tensor-core kernel (which falls back by itself for shapes
     it does not cover, e.g. more than 8 query columns per kv head)."""
     monkeypatch.setenv("OMNI_QATTN_KERNEL", request.param)
-    return request.param
+    yield request.param
+    from omnistack_rs_b200 import _lib
+    _lib.check_device_status(torch.device("cuda:0"))      # no bounded wait may have expired
 
 
 def attn_mod():
