@@ -147,7 +147,7 @@ __host__ __device__ constexpr uint32_t sign_half2(uint32_t bit0, uint32_t bit1) 
 //   1: int8 MMA, A = -bit built in registers (multiply spreads 4 bits to the 4 byte MSBs, PRMT
 //      replicates them), B = q.g quantised to int8 per column; no shared-memory traffic.
 #ifndef OMNI_SIGN_INT8
-#define OMNI_SIGN_INT8 0
+#define OMNI_SIGN_INT8 1
 #endif
 struct SignB {
 #if OMNI_SIGN_INT8
@@ -168,7 +168,9 @@ __device__ __forceinline__ void imma_s8(int (&d)[4], uint32_t a0, uint32_t a1, u
 template <int LOW>
 __device__ __forceinline__ uint32_t neg_bits_s8(uint32_t s) {
     const uint32_t spread = (s & (0xFu << LOW)) * (LOW == 0 ? 0x10204080u : 0x01020408u);   // bit j -> MSB of byte j
-    return __byte_perm(spread, 0, 0xBA98);                                                  // replicate each MSB
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %1, 0xBA98;\n" : "=r"(r) : "r"(spread));   // selector MSBs: replicate the byte's sign bit
+    return r;                                                  // replicate each MSB
 }
 
 // ---- mbarrier / TMA ---------------------------------------------------------------------
@@ -374,7 +376,8 @@ struct Ring {
 __device__ __forceinline__ void ring_issue(Ring& r, const CUtensorMap* mk, const CUtensorMap* mv, int32_t row, int lane) {
     if (lane == 0) {
         const uint32_t bar = r.bar0 + 8 * r.fill, dst = r.stage0 + r.fill * kStageBytes;
-        fence_proxy_async();                     // earlier reads of this stage are ordered before the refill
+        // no proxy fence is needed before the refill: every lane has already consumed (not merely issued)
+        // its reads of this stage, and the caller's __syncwarp() ordered that before this point
         mbar_expect_tx(bar, kStageBytes);
         tma_load_rows(dst, mk, row, bar);
         tma_load_rows(dst + kStageKeys * kNibBytes, mv, row, bar);
