@@ -47,7 +47,7 @@ BYTES_PER_KEY = 64 + 8 + 4 + 64          # K nibbles + K sign bytes + K norm + V
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per (user, kv head, key) of the decode kernel from the ncu capture summarised in
 # profiles/ (None until a capture exists); scaled to a full launch by the keys it processes.
-NCU_DRAM_BYTES_PER_KEY = None
+NCU_DRAM_BYTES_PER_KEY = 150.2   # profiles/qattn_mma_kernel_serving.md: (10.062 GB read + 0.021 GB written) / 67.1 M keys
 
 
 def measured_peak():
@@ -256,10 +256,21 @@ def run_ours(args):
     print(json.dumps(line))
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs are meant to use every core they may."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_baseline(Hq, Hkv, S, lens, budget_s=15.0, n_users=2):
     """Time the CPU oracle (port of the reference's torch path) on ``n_users`` users of the
     workload's shape; repeated until about ``budget_s`` seconds have been spent."""
     import oracle as orc
+    use_all_host_threads()
     gen = torch.Generator().manual_seed(7)
     Su = S if lens is None else int(lens[:n_users].max())
     cb = orc.lloyd_max_fit(torch.randn(1 << 14, generator=gen), max_iters=20)
@@ -285,6 +296,7 @@ def run_reference(args):
     if rank != 0:
         return
     import oracle as orc
+    use_all_host_threads()
     desc, Hq, Hkv, S, users = WORKLOADS[args.workload]
     n_users = args.ref_users
     gen = torch.Generator().manual_seed(7)
