@@ -9,6 +9,8 @@
 //     fp32 residuals, i.e. the mathematically exact sign up to 2^-53 relative error --
 //     the reference's sgemm agrees whenever its own fp32 rounding does not decide the bit.
 #include "common.cuh"
+#include "codec_fast.cuh"
+#include <cstdlib>
 
 namespace omni {
 
@@ -182,11 +184,23 @@ static int32_t launch_quantize(const CodecArgs& a, int rotate, cudaStream_t st) 
     return check_cuda(cudaGetLastError(), "quantize_kernel launch");
 }
 
+// OMNI_QUANT_KERNEL=scan forces the one-row-per-warp kernel (tests and profiling); default: the fast
+// kernel whenever the call fits it.
+static bool fast_kernel_allowed() {
+    const char* e = getenv("OMNI_QUANT_KERNEL");
+    return !(e && e[0] == 's');
+}
+
 static int32_t quantize_common(CodecArgs& a, int32_t dtype, int32_t rotate, void* stream) {
     const DeviceTables* tb = tables_for_current_device();
     if (!tb) return OMNI_ERR_NOT_INIT;
     a.g_rows = tb->rows; a.g_cols = tb->cols;
     cudaStream_t st = (cudaStream_t)stream;
+    if (!a.row_seeded && fast_kernel_allowed()) {
+        FastQuantArgs f{a.x, a.xs_b, a.xs_h, a.xs_t, a.codebooks, a.cb_per_head, a.user_ids, a.user_id, a.B, a.H, a.T,
+                        a.nib, a.qjl, a.norms, a.os_b, a.os_h, a.out_offsets, a.out_offset, a.g_rows};
+        if (fast_quantize_eligible(f, dtype)) return launch_fast_quantize(f, dtype, rotate, st);
+    }
     switch (dtype) {
         case OMNI_F32:  return launch_quantize<OMNI_F32>(a, rotate, st);
         case OMNI_BF16: return launch_quantize<OMNI_BF16>(a, rotate, st);

@@ -1,0 +1,415 @@
+// Fast rotate + quantize kernel of the KV-cache codec (sm_100a).
+//
+// Layout: a warp takes 8 consecutive tokens of one (user, head) at a time; row r of the group is
+// owned by lanes 4r..4r+3 and lane t of those holds the 32 contiguous elements d = 32t..32t+31.
+//   * rotation: five butterfly stages inside the thread, two across lanes (xor 1, xor 2), in the
+//     reference's stage order h = 1..64 with one rounding per add/subtract (the cross-lane stages use
+//     fma(+-1, mine, partner), which rounds exactly like the add or subtract it replaces);
+//   * INT4 code: a 32-cell uniform grid over the threshold range gives a base code, one exact fp32
+//     threshold compare settles base / base+1.  Thresholds and cell bases are derived per codebook at
+//     kernel start by bisection against the defining first-index argmin of |y - c|, so the result is
+//     the reference's code bit for bit; inputs outside the range where that shortcut is proven
+//     (|y| beyond `guard`, or a codebook the grid cannot resolve) take the defining scan instead;
+//   * QJL sign bits: the residual row is scaled by a power of two to 15-bit integers and split into a
+//     signed high and an unsigned low byte; the 64 x 128 +-1 projection runs on the int8 tensor cores
+//     (mma.sync m16n8k32, G as the A operand, the 8 rows as the 8 columns of B).  The integer sum
+//     differs from the exact scaled sum by at most 64, so |sum| > 64 decides the sign rigorously; the
+//     few projections inside that band are recomputed exactly in fp64;
+//   * packed outputs: 16-byte nibble stores per lane (64 contiguous bytes per row), 2-byte sign stores.
+#include "codec_fast.cuh"
+
+namespace omni {
+
+constexpr int kFqWarps = 8;
+constexpr int kFqMaxHeads = 32;
+
+// Per-head quantiser tables in shared memory.
+struct HeadTables {
+    float thr[20];          // thr[c], c = 1..15: smallest fp32 y whose code is >= c; thr[16] = +inf
+    float cb[16];
+    uint8_t cell[32];       // code at the low end of each grid cell
+    float inv32, off32;     // cell(y) = rn(31 * sat(y * inv32 + off32))
+    float guard;            // |y| <= guard: the threshold shortcut is valid
+    int valid;              // 0: this codebook always takes the defining scan
+    int pad[4];
+};
+static_assert(sizeof(HeadTables) % 16 == 0, "HeadTables must keep 16-byte alignment in an array");
+
+__device__ __forceinline__ int order_key(float x) {           // monotone float -> int
+    const int b = __float_as_int(x);
+    return b >= 0 ? b : (int)(0x80000000u - (uint32_t)b);
+}
+__device__ __forceinline__ float order_unkey(int k) {
+    return __int_as_float(k >= 0 ? k : (int)(0x80000000u - (uint32_t)k));
+}
+// the reference's code: first index minimising |y - c| in fp32
+__device__ __forceinline__ int code_by_scan(float y, const float* cb) {
+    float best = fabsf(__fsub_rn(y, cb[0]));
+    int code = 0;
+#pragma unroll
+    for (int c = 1; c < 16; ++c) {
+        const float d = fabsf(__fsub_rn(y, cb[c]));
+        if (d < best) { best = d; code = c; }
+    }
+    return code;
+}
+__device__ __forceinline__ int cell_of(float y, float inv32, float off32) {
+    const float u = __saturatef(fmaf(y, inv32, off32));
+    return __float_as_int(fmaf(u, 31.f, 12582912.f)) & 31;
+}
+
+// One warp derives the tables of one codebook (lane = grid cell, lanes 1..15 also own a threshold).
+__device__ void build_head_tables(HeadTables& ht, const float* cb_global, int lane) {
+    if (lane < 16) ht.cb[lane] = __ldg(cb_global + lane);
+    __syncwarp();
+    const float c_me = ht.cb[lane & 15], c_prev = ht.cb[(lane + 15) & 15];
+    const bool ordered = (lane == 0 || lane >= 16) ? true : (c_me > c_prev);
+    const bool finite = isfinite(c_me);
+    float gap = (lane >= 1 && lane < 16) ? c_me - c_prev : INFINITY;
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) gap = fminf(gap, __shfl_xor_sync(kFullMask, gap, m));
+    const float maxabs = fmaxf(fabsf(ht.cb[0]), fabsf(ht.cb[15]));
+    const float guard = gap * 1048576.f;
+    bool ok = __all_sync(kFullMask, ordered && finite) && gap > 0.f && isfinite(guard) && guard >= 4.f * maxabs;
+    if (!ok) {                                       // uniform: every element of this head is scanned
+        if (lane == 0) { ht.valid = 0; ht.guard = -1.f; ht.inv32 = 0.f; ht.off32 = 0.f; }
+        __syncwarp();
+        return;
+    }
+    // thresholds: bisection between cb[c-1] (code c-1) and cb[c] (code c)
+    if (lane >= 1 && lane < 16) {
+        int lo = order_key(c_prev), hi = order_key(c_me);
+        while ((int64_t)hi - lo > 1) {
+            const int mid = (int)(((int64_t)lo + hi) >> 1);
+            if (code_by_scan(order_unkey(mid), ht.cb) >= lane) hi = mid; else lo = mid;
+        }
+        ht.thr[lane] = order_unkey(hi);
+    }
+    if (lane == 16) ht.thr[16] = INFINITY;
+    if (lane == 0) ht.thr[0] = -INFINITY;
+    __syncwarp();
+    const float t1 = ht.thr[1], t15 = ht.thr[15];
+    const float margin = (t15 - t1) * (1.f / 29.f);
+    const float lo_y = t1 - margin, hi_y = t15 + margin;
+    const float inv32 = 1.f / (hi_y - lo_y), off32 = -lo_y * inv32;
+    // cell u: a = smallest y in [-guard, guard] with cell_of(y) >= u; its code is the cell's base
+    float a = -guard;
+    if (lane > 0) {
+        int lo = order_key(-guard), hi = order_key(guard);          // cell(lo) = 0 < lane <= cell(hi) = 31
+        while ((int64_t)hi - lo > 1) {                               // the key range spans more than 2^31
+            const int mid = (int)(((int64_t)lo + hi) >> 1);
+            if (cell_of(order_unkey(mid), inv32, off32) >= lane) hi = mid; else lo = mid;
+        }
+        a = order_unkey(hi);
+    }
+    const int base = code_by_scan(a, ht.cb);
+    // last y of the cell = predecessor of the next cell's first y (guard for the last cell)
+    const float a_next = __shfl_down_sync(kFullMask, a, 1);
+    const float b = (lane == 31) ? guard : order_unkey(order_key(a_next) - 1);
+    const int top = code_by_scan(b, ht.cb);
+    ok = __all_sync(kFullMask, top - base <= 1 && top >= base) &&
+         cell_of(-guard, inv32, off32) == 0 && cell_of(guard, inv32, off32) == 31;
+    ht.cell[lane] = (uint8_t)base;
+    if (lane == 0) { ht.valid = ok ? 1 : 0; ht.guard = ok ? guard : -1.f; ht.inv32 = inv32; ht.off32 = off32; }
+    __syncwarp();
+}
+
+// ---- small PTX helpers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t prmt_sign_bytes(uint32_t x) {     // each byte -> 0xFF if its MSB is set, else 0x00
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %1, 0xBA98;\n" : "=r"(r) : "r"(x));
+    return r;
+}
+// four int8 of +-1 from 4 bits of a Rademacher row: bit 1 -> +1, bit 0 -> -1 (bits at LOW..LOW+3 of w)
+template <int LOW>
+__device__ __forceinline__ uint32_t pm1_bytes(uint32_t w) {
+    const uint32_t spread = (~w & (0xFu << LOW)) * (LOW == 0 ? 0x10204080u : 0x01020408u);
+    return prmt_sign_bytes(spread) | 0x01010101u;
+}
+__device__ __forceinline__ void imma_s8s8(int (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_s8u8(int (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+// gather the bits at positions 4k + s (k = 0..7) of w into one byte
+__device__ __forceinline__ uint32_t every_fourth_bit(uint32_t w, int s) {
+    uint32_t x = (w >> s) & 0x11111111u;
+    x = (x | (x >> 3)) & 0x03030303u;
+    x = (x | (x >> 6)) & 0x000F000Fu;
+    x = (x | (x >> 12)) & 0xFFu;
+    return x;
+}
+
+// load 32 consecutive elements as fp32
+template <int DT> struct Row32;
+template <> struct Row32<OMNI_F32> {
+    static __device__ __forceinline__ void load(const void* p, int64_t i, float (&y)[32]) {
+        const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { const float4 v = __ldg(q + k); y[4 * k] = v.x; y[4 * k + 1] = v.y; y[4 * k + 2] = v.z; y[4 * k + 3] = v.w; }
+    }
+    static __device__ __forceinline__ void round_pair(float& a, float& b) {}
+};
+template <> struct Row32<OMNI_BF16> {
+    static __device__ __forceinline__ void load(const void* p, int64_t i, float (&y)[32]) {
+        const uint4* q = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint4 v = __ldg(q + k);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                y[8 * k + 2 * j] = __uint_as_float(w[j] << 16);
+                y[8 * k + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            }
+        }
+    }
+    static __device__ __forceinline__ void round_pair(float& a, float& b) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+        a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u);
+    }
+};
+template <> struct Row32<OMNI_F16> {
+    static __device__ __forceinline__ void load(const void* p, int64_t i, float (&y)[32]) {
+        const uint4* q = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p) + i);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint4 v = __ldg(q + k);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                y[8 * k + 2 * j] = f.x; y[8 * k + 2 * j + 1] = f.y;
+            }
+        }
+    }
+    static __device__ __forceinline__ void round_pair(float& a, float& b) {
+        const float2 f = __half22float2(__floats2half2_rn(a, b));
+        a = f.x; b = f.y;
+    }
+};
+
+template <int DT, bool ROTATE>
+__global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQuantArgs a) {
+    extern __shared__ __align__(16) unsigned char fq_smem[];
+    const int n_tabs = a.cb_per_head ? a.H : 1;
+    HeadTables* tabs = reinterpret_cast<HeadTables*>(fq_smem);
+    uint4* gfrag_all = reinterpret_cast<uint4*>(fq_smem + sizeof(HeadTables) * n_tabs);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    uint4* gfrag = gfrag_all + (size_t)warp * 16 * 32 + lane;      // this lane's 16 A fragments, 32 uint4 apart
+
+    for (int h = warp; h < n_tabs; h += kFqWarps) build_head_tables(tabs[h], a.codebooks + h * 16, lane);
+    __syncthreads();
+
+    const int64_t n_pairs = a.B * a.H;
+    for (int64_t p = (int64_t)blockIdx.x * kFqWarps + warp; p < n_pairs; p += (int64_t)gridDim.x * kFqWarps) {
+        const int64_t b = p / a.H;
+        const int h = (int)(p % a.H);
+        const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
+        const int seed = seed_of(uid, h);
+        const uint32_t* grow = a.g_rows + (size_t)seed * kQjlDim * 4;
+        // A fragments of G for this lane: m-tile mt (16 projections), k-step ks (8 of this lane's dims)
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            const uint32_t w0 = __ldg(grow + (16 * mt + g) * 4 + t), w1 = __ldg(grow + (16 * mt + g + 8) * 4 + t);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint32_t b0 = w0 >> (8 * ks), b1 = w1 >> (8 * ks);
+                gfrag[(mt * 4 + ks) * 32] = make_uint4(pm1_bytes<0>(b0), pm1_bytes<0>(b1), pm1_bytes<4>(b0), pm1_bytes<4>(b1));
+            }
+        }
+        const HeadTables& ht = tabs[a.cb_per_head ? h : 0];
+        const float inv32 = ht.inv32, off32 = ht.off32, guard = ht.guard;
+        const int64_t in_base = b * a.xs_b + (int64_t)h * a.xs_h + 32 * t;
+        const int64_t out_base = b * a.os_b + (int64_t)h * a.os_h + (a.out_offsets ? a.out_offsets[b] : a.out_offset);
+
+        for (int64_t t0 = 0; t0 < a.T; t0 += 8) {
+            const int64_t tr = t0 + g;
+            const bool active = tr < a.T;
+            const int64_t trc = active ? tr : a.T - 1;
+            float y[32];
+            Row32<DT>::load(a.x, in_base + trc * a.xs_t, y);
+            if (ROTATE) {
+#pragma unroll
+                for (int hh = 1; hh < 32; hh <<= 1) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if ((i & hh) == 0) {
+                            const float u = y[i], v = y[i | hh];
+                            y[i] = __fadd_rn(u, v);
+                            y[i | hh] = __fsub_rn(u, v);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int m = 1; m <= 2; m <<= 1) {
+                    const float sgn = (t & m) ? -1.f : 1.f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float o = __shfl_xor_sync(kFullMask, y[i], m);
+                        y[i] = __fmaf_rn(sgn, y[i], o);
+                    }
+                }
+                const float sc = __uint_as_float(OMNI_WHT_SCALE_BITS);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) y[i] = __fmul_rn(y[i], sc);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) Row32<DT>::round_pair(y[i], y[i + 1]);
+            }
+            // ---- INT4 codes and residual (y becomes the residual) ---------------------------------
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(y[i]));
+            uint32_t codes[4] = {0u, 0u, 0u, 0u};
+            if (__any_sync(kFullMask, !(amax <= guard))) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int c = code_by_scan(y[i], ht.cb);
+                    codes[i >> 3] |= (uint32_t)c << (4 * (i & 7));
+                    y[i] = __fsub_rn(y[i], ht.cb[c]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int base = ht.cell[cell_of(y[i], inv32, off32)];
+                    const int c = base + (y[i] >= ht.thr[base + 1] ? 1 : 0);
+                    codes[i >> 3] |= (uint32_t)c << (4 * (i & 7));
+                    y[i] = __fsub_rn(y[i], ht.cb[c]);
+                }
+            }
+            // ---- residual norm and fixed-point scale ------------------------------------------------
+            float ss = 0.f, emax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { ss = fmaf(y[i], y[i], ss); emax = fmaxf(emax, fabsf(y[i])); }
+            ss += __shfl_xor_sync(kFullMask, ss, 1);   ss += __shfl_xor_sync(kFullMask, ss, 2);
+            emax = fmaxf(emax, __shfl_xor_sync(kFullMask, emax, 1));
+            emax = fmaxf(emax, __shfl_xor_sync(kFullMask, emax, 2));
+            const int E = (__float_as_uint(emax) >> 23) & 0xFF;
+            // rows whose largest residual is 0 / tiny / inf, or that hold a NaN (then the sum of squares is not
+            // finite), cannot be scaled to integers: all their signs are recomputed exactly
+            const bool degenerate = (E < 16) || (E == 255) || !(ss < INFINITY);
+            // scale = 2^(141-E) * (1 - 2^-9): emax * scale lies in [2^14 - 32, 2^15 - 64), so the rounded integers fit int16.
+            // The scale need not be a power of two: the fused multiply-add below rounds e*scale + magic once.
+            const float scale = degenerate ? 0.f : __uint_as_float(((uint32_t)(267 - E) << 23) | 0x7F8000u);
+            // ---- projections on the int8 tensor cores -------------------------------------------------
+            int chi[4][4], clo[4][4];
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { chi[mt][j] = 0; clo[mt][j] = 0; }
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                uint32_t v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(fmaf(y[8 * ks + k], scale, 12582912.f));   // low 16 bits = int16
+                const uint32_t p01 = __byte_perm(v[0], v[1], 0x5140), p23 = __byte_perm(v[2], v[3], 0x5140);
+                const uint32_t p45 = __byte_perm(v[4], v[5], 0x5140), p67 = __byte_perm(v[6], v[7], 0x5140);
+                const uint32_t lo0 = __byte_perm(p01, p23, 0x5410), hi0 = __byte_perm(p01, p23, 0x7632);
+                const uint32_t lo1 = __byte_perm(p45, p67, 0x5410), hi1 = __byte_perm(p45, p67, 0x7632);
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt) {
+                    const uint4 af = gfrag[(mt * 4 + ks) * 32];
+                    imma_s8s8(chi[mt], af, hi0, hi1);
+                    imma_s8u8(clo[mt], af, lo0, lo1);
+                }
+            }
+            // ---- sign / ambiguity bits: C element (mt, j) = projection 16mt + g + 8(j>>1) of row 2t + (j&1) ----
+            const bool deg0 = __shfl_sync(kFullMask, (int)degenerate, 8 * t) != 0;         // row 2t   (lanes 8t..)
+            const bool deg1 = __shfl_sync(kFullMask, (int)degenerate, 8 * t + 4) != 0;     // row 2t+1
+            uint32_t word_s = 0u, word_a = 0u;                 // lane k < 16 keeps ballot word k = 4mt + j
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int sum = chi[mt][j] * 256 + clo[mt][j];
+                    const uint32_t bs = __ballot_sync(kFullMask, sum >= 0);
+                    const uint32_t ba = __ballot_sync(kFullMask, (sum <= 64 && sum >= -64) || ((j & 1) ? deg1 : deg0));
+                    if (lane == mt * 4 + j) { word_s = bs; word_a = ba; }
+                }
+            }
+            // lane (row g, quarter t) owns projections 16t .. 16t+15: m-tile t, halves j>>1 = 0, 1, column parity g&1
+            uint32_t bits16, amb16;
+            {
+                const int src0 = 4 * t + (g & 1), src1 = src0 + 2;
+                const uint32_t s0 = __shfl_sync(kFullMask, word_s, src0), s1 = __shfl_sync(kFullMask, word_s, src1);
+                const uint32_t a0 = __shfl_sync(kFullMask, word_a, src0), a1 = __shfl_sync(kFullMask, word_a, src1);
+                const int sh = g >> 1;                          // the C owner of this row's columns has t'' = g >> 1
+                bits16 = every_fourth_bit(s0, sh) | (every_fourth_bit(s1, sh) << 8);
+                amb16 = every_fourth_bit(a0, sh) | (every_fourth_bit(a1, sh) << 8);
+            }
+            if (!active) amb16 = 0u;
+            // ---- exact recomputation of the undecided projections, one per row at a time ------------------
+            uint64_t pending = (uint64_t)__shfl_sync(kFullMask, amb16, 4 * g) |
+                               ((uint64_t)__shfl_sync(kFullMask, amb16, 4 * g + 1) << 16) |
+                               ((uint64_t)__shfl_sync(kFullMask, amb16, 4 * g + 2) << 32) |
+                               ((uint64_t)__shfl_sync(kFullMask, amb16, 4 * g + 3) << 48);
+            while (__any_sync(kFullMask, pending != 0ull)) {
+                const bool have = pending != 0ull;
+                const int pi = have ? __ffsll((long long)pending) - 1 : 0;
+                if (have) pending &= pending - 1ull;
+                const uint32_t gw = __ldg(grow + pi * 4 + t);
+                double acc = 0.0;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { const double ev = (double)y[i]; acc += ((gw >> i) & 1u) ? ev : -ev; }
+                acc += __shfl_xor_sync(kFullMask, acc, 1);
+                acc += __shfl_xor_sync(kFullMask, acc, 2);
+                if (have && t == (pi >> 4)) {
+                    const uint32_t m = 1u << (pi & 15);
+                    bits16 = (acc >= 0.0) ? (bits16 | m) : (bits16 & ~m);
+                }
+            }
+            // ---- stores ----------------------------------------------------------------------------------
+            if (active) {
+                const int64_t ro = out_base + tr;
+                *reinterpret_cast<uint4*>(a.nib + ro * kNibBytes + 16 * t) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+                *reinterpret_cast<uint16_t*>(a.qjl + ro * kQjlBytes + 2 * t) = (uint16_t)bits16;
+                if (t == 0) a.norms[ro] = sqrtf(ss);
+            }
+        }
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+static bool fq_aligned(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) % n) == 0; }
+
+// true when the fast kernel covers this call (shape, alignment); the caller falls back otherwise
+bool fast_quantize_eligible(const FastQuantArgs& a, int dtype) {
+    const int64_t esz = dtype == OMNI_F32 ? 4 : 2;
+    const int64_t vec = 16 / esz;
+    if (a.cb_per_head && a.H > kFqMaxHeads) return false;
+    if (!fq_aligned(a.x, 16) || a.xs_b % vec || a.xs_h % vec || a.xs_t % vec) return false;
+    if (!fq_aligned(a.nib, 16) || !fq_aligned(a.qjl, 2)) return false;
+    return a.T > 0;
+}
+
+template <int DT>
+static int32_t launch_fast_t(const FastQuantArgs& a, int rotate, cudaStream_t st) {
+    int dev = 0, sms = 148;
+    OMNI_CUDA(cudaGetDevice(&dev));
+    OMNI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int n_tabs = a.cb_per_head ? a.H : 1;
+    const size_t smem = sizeof(HeadTables) * n_tabs + (size_t)kFqWarps * 16 * 32 * sizeof(uint4);
+    const int64_t pairs = a.B * a.H;
+    int64_t blocks = (pairs + kFqWarps - 1) / kFqWarps;
+    if (blocks > 2 * sms) blocks = 2 * sms;
+    auto kern = rotate ? fast_quantize_kernel<DT, true> : fast_quantize_kernel<DT, false>;
+    OMNI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<(unsigned)blocks, kFqWarps * 32, smem, st>>>(a);
+    return check_cuda(cudaGetLastError(), "fast_quantize_kernel launch");
+}
+
+int32_t launch_fast_quantize(const FastQuantArgs& a, int dtype, int rotate, cudaStream_t st) {
+    switch (dtype) {
+        case OMNI_F32:  return launch_fast_t<OMNI_F32>(a, rotate, st);
+        case OMNI_BF16: return launch_fast_t<OMNI_BF16>(a, rotate, st);
+        case OMNI_F16:  return launch_fast_t<OMNI_F16>(a, rotate, st);
+    }
+    return set_error(OMNI_ERR_ARG, "unknown dtype code %d", dtype);
+}
+
+}  // namespace omni

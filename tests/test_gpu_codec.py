@@ -20,6 +20,14 @@ def dev():
     return torch.device("cuda:0")
 
 
+@pytest.fixture(autouse=True, params=["fast", "scan"])
+def quant_kernel_choice(request, monkeypatch):
+    """Every case runs once per quantize kernel: the 8-rows-per-warp tensor-core kernel (default)
+    and the one-row-per-warp scan kernel that OMNI_QUANT_KERNEL=scan forces."""
+    monkeypatch.setenv("OMNI_QUANT_KERNEL", request.param)
+    return request.param
+
+
 def k():
     from omnistack_rs_b200.kernels import quantize, hadamard
     return quantize, hadamard
