@@ -173,7 +173,9 @@ int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
  * resident): copies q_host -> q_stage (device), runs omni_qattn_decode, copies the
  * result out_stage (device) -> out_host, in `n_chunks` user chunks pipelined over
  * two internal streams, and returns after everything has completed.  q_host/out_host
- * should be page-locked.  Remaining arguments as in omni_qattn_decode (n_splits = 1). */
+ * should be page-locked.  Remaining arguments as in omni_qattn_decode; with n_splits > 1 the workspace
+ * must hold two slices of omni_qattn_workspace_bytes(ceil(B / n_chunks), Hq, T, n_splits) bytes (one per
+ * internal stream). */
 int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, void* q_stage,
                                const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
                                const uint8_t* v_nib,
@@ -183,7 +185,8 @@ int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, void* q_stag
                                int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                                int64_t ks_b, int64_t ks_h,
                                float scale, int32_t with_qjl,
-                               float* out_stage, float* out_host, int32_t n_chunks);
+                               float* out_stage, float* out_host, int32_t n_chunks,
+                               int32_t n_splits, void* workspace, size_t workspace_bytes);
 
 #ifdef __cplusplus
 }

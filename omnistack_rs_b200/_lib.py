@@ -39,7 +39,8 @@ SIGNATURES = {
                                          _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
                                          _vp, _vp]),
     "omni_qattn_decode_host": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
-                                      _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _vp, _vp, _i32]),
+                                      _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _vp, _vp, _i32,
+                                      _i32, _vp, _sz]),
 }
 
 _lock = threading.Lock()

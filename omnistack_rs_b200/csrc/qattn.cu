@@ -335,7 +335,8 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
                                           const int32_t* seq_lens, const int32_t* cache_slots,
                                           int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                                           int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
-                                          float* out_stage, float* out_host, int32_t n_chunks) {
+                                          float* out_stage, float* out_host, int32_t n_chunks,
+                                          int32_t n_splits, void* workspace, size_t workspace_bytes) {
     const DeviceTables* tb = tables_for_current_device();
     if (!tb) return OMNI_ERR_NOT_INIT;
     OMNI_REQUIRE(q_host && q_stage && out_stage && out_host, OMNI_ERR_ARG, "qattn_decode_host: NULL buffer");
@@ -352,6 +353,12 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
     }
     const size_t qsz = q_dtype == OMNI_F32 ? 4 : 2;
     const int64_t per = (B + n_chunks - 1) / n_chunks;
+    // chunks alternate between two streams, so split-K needs one workspace slice per stream
+    const size_t ws_chunk = omni_qattn_workspace_bytes(per, Hq, T, n_splits);
+    OMNI_REQUIRE(n_splits >= 1, OMNI_ERR_ARG, "qattn_decode_host: n_splits < 1");
+    OMNI_REQUIRE(n_splits == 1 || (workspace && workspace_bytes >= 2 * ws_chunk), OMNI_ERR_ARG,
+                 "qattn_decode_host: %d splits need a workspace of %zu bytes (two chunk slices), got %zu",
+                 n_splits, 2 * ws_chunk, workspace_bytes);
     int c = 0;
     for (int64_t b0 = 0; b0 < B; b0 += per, ++c) {
         const int64_t nb = (b0 + per <= B) ? per : B - b0;
@@ -366,8 +373,10 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
                    k_norms ? k_norms + row0 : nullptr, v_nib + row0 * kNibBytes,
                    codebooks, cb_per_head, user_ids ? user_ids + b0 : nullptr, user_id,
                    seq_lens ? seq_lens + b0 : nullptr, cache_slots ? cache_slots + b0 : nullptr,
-                   nb, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, 0, 0, 1, nullptr, out_stage + qoff, tb->rows, nullptr};
-        int32_t stc = validate(a, 0);
+                   nb, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, 0, 0, n_splits,
+                   n_splits > 1 ? reinterpret_cast<float*>((char*)workspace + (size_t)(c & 1) * ws_chunk) : nullptr,
+                   out_stage + qoff, tb->rows, nullptr};
+        int32_t stc = validate(a, ws_chunk);
         if (stc == OMNI_OK) stc = launch(a, st);
         if (stc != OMNI_OK) { cudaStreamSynchronize(g_hs[dev].s[0]); cudaStreamSynchronize(g_hs[dev].s[1]); return stc; }
         OMNI_CUDA(cudaMemcpyAsync(out_host + qoff, out_stage + qoff, (size_t)nb * Hq * T * kHeadDim * sizeof(float),

@@ -57,13 +57,17 @@ def _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha):
     return torch.where(active.view(B, 1, 1, 1), q.float() + delta, q.float())
 
 
-def _auto_splits(B: int, Hq: int, T: int, S: int) -> int:
-    """Enough (user, head, token, split) units to fill the GPU a few times over."""
-    units = B * Hq * T
-    target = _SM_COUNT * 16 * 2
+def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int) -> int:
+    """Key-axis splits that give every resident warp several work units.  The tensor-core kernel
+    works per (user, kv head) (12 warps on each of 148 SMs); the lane-per-key kernel per
+    (user, query head, token)."""
+    if (Hq // Hkv) * T <= 8 and S >= 128:
+        units, target = B * Hkv, _SM_COUNT * 12 * 8
+    else:
+        units, target = B * Hq * T, _SM_COUNT * 16 * 2
     if units >= target or S <= 256:
         return 1
-    return int(max(1, min(target // max(units, 1), S // 128, 64)))
+    return int(max(1, min(-(-target // max(units, 1)), S // 256, 64)))
 
 
 def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
@@ -88,7 +92,7 @@ def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, w
     lens = None if seq_lens is None else seq_lens.to(device=dev, dtype=torch.int32).contiguous()
     slots = None if cache_slots is None else cache_slots.to(device=dev, dtype=torch.int32).contiguous()
     if n_splits is None:
-        n_splits = _auto_splits(B, Hq, T, S)
+        n_splits = _auto_splits(B, Hq, Hkv, T, S)
     ws, ws_bytes = None, 0
     if n_splits > 1:
         ws_bytes = lib.omni_qattn_workspace_bytes(B, Hq, T, n_splits)

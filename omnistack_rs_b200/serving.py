@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 from .kernels.quantize import _NBYTES_NIBBLE, _NBYTES_QJL, _prep_codebooks, rotate_quantize_append
-from .kernels.fused_attention import _qattn
+from .kernels.fused_attention import _qattn, _auto_splits
 
 HEAD_DIM = 128
 
@@ -110,7 +110,7 @@ class HostDecodeStep:
 
     def __init__(self, k_nib, k_qjl, k_norms, v_nib, codebooks, n_heads: int, batch: int, q_dtype=torch.bfloat16,
                  user_id=0, seq_lens=None, cache_slots=None, scale: Optional[float] = None, with_qjl: bool = True,
-                 T: int = 1, n_chunks: int = 8):
+                 T: int = 1, n_chunks: Optional[int] = None, n_splits: Optional[int] = None):
         self.dev = _lib.require_cuda(k_nib, k_qjl, k_norms, v_nib)
         self.lib = _lib.ensure_init(self.dev)
         self.k_nib, self.k_qjl, self.k_norms, self.v_nib = k_nib, k_qjl, k_norms, v_nib
@@ -126,7 +126,13 @@ class HostDecodeStep:
         self.lens = None if seq_lens is None else seq_lens.to(device=self.dev, dtype=torch.int32).contiguous()
         self.slots = None if cache_slots is None else cache_slots.to(device=self.dev, dtype=torch.int32).contiguous()
         self.scale = float(scale if scale is not None else 1.0 / math.sqrt(HEAD_DIM))
+        if n_chunks is None:                       # chunks of at least ~2k users keep every SM busy
+            n_chunks = max(1, min(8, batch // 2048))
         self.with_qjl, self.n_chunks = int(bool(with_qjl)), int(n_chunks)
+        per_chunk = -(-batch // self.n_chunks)
+        self.n_splits = int(n_splits) if n_splits is not None else _auto_splits(per_chunk, n_heads, self.Hkv, T, self.S)
+        self.ws_bytes = 2 * self.lib.omni_qattn_workspace_bytes(per_chunk, n_heads, T, self.n_splits)
+        self.ws = torch.empty(max(self.ws_bytes // 4, 1), dtype=torch.float32, device=self.dev)
         shape = (batch, n_heads, T, HEAD_DIM)
         self.q_stage = torch.empty(shape, dtype=q_dtype, device=self.dev)
         self.out_stage = torch.empty(shape, dtype=torch.float32, device=self.dev)
@@ -147,5 +153,6 @@ class HostDecodeStep:
                 _lib.ptr(self.k_nib), _lib.ptr(self.k_qjl), _lib.ptr(self.k_norms), _lib.ptr(self.v_nib),
                 _lib.ptr(self.cb), self.per_head, _lib.ptr(self.ids), self.uid, _lib.ptr(self.lens), _lib.ptr(self.slots),
                 self.B, self.Hq, self.Hkv, self.T, self.S, self.Hkv * self.S, self.S, self.scale, self.with_qjl,
-                _lib.ptr(self.out_stage), _lib.ptr(self.out_host), self.n_chunks))
+                _lib.ptr(self.out_stage), _lib.ptr(self.out_host), self.n_chunks,
+                self.n_splits, _lib.ptr(self.ws), self.ws_bytes))
         return self.out_host
