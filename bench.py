@@ -42,6 +42,8 @@ WORKLOADS = {
     "serve": ("config4-box-serving-shard: 16384 users/GPU x 32 kv heads x 2048 keys, 1 bf16 query/user/step", 32, 32, 2048, USERS_PER_GPU),
     "decode64": ("config1: 64 users x 8 heads x 50 keys", 8, 8, 50, 64),
     "gqa": ("config2: 256 users, 32 q / 8 kv heads, context U[1024,8192]", 32, 8, 8192, 256),
+    # quantize-append (reporting only): 8 kv heads, 256 new bf16 tokens per user, K and V
+    "append": ("config3: 4096 users x 256 new tokens x 8 heads, bf16 K and V, N(0,1) with 1% x10", 8, 8, 256, 4096),
 }
 BYTES_PER_KEY = 64 + 8 + 4 + 64          # K nibbles + K sign bytes + K norm + V nibbles
 FALLBACK_HBM_GBS = 6650.0
@@ -271,6 +273,113 @@ def use_all_host_threads():
     return torch.get_num_threads()
 
 
+def run_append(args):
+    """Quantize-append workload (benchmark configuration 3): every step rotates and quantizes 256 new
+    bf16 K and V tokens per user into the users' packed caches.  Metric: tokens/s."""
+    import torch.distributed as dist
+    import oracle as orc
+    from omnistack_rs_b200 import _lib
+    from omnistack_rs_b200.kernels.quantize import _quantize_into
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    desc, _, H, T, users = WORKLOADS["append"]
+    if args.users:
+        users = args.users
+    gen = torch.Generator(device=dev).manual_seed(99 + rank)
+
+    def heavy_tail():
+        x = torch.randn(users, H, T, 128, generator=gen, device=dev)
+        return torch.where(torch.rand(users, H, T, 128, generator=gen, device=dev) < 0.01, x * 10, x).to(torch.bfloat16)
+
+    xk, xv = heavy_tail(), heavy_tail()
+    cb = torch.tensor([-2.733, -2.069, -1.618, -1.256, -0.9424, -0.6568, -0.3881, -0.1284,
+                       0.1284, 0.3881, 0.6568, 0.9424, 1.256, 1.618, 2.069, 2.733], device=dev)
+    ids = torch.arange(users, dtype=torch.int32, device=dev) + rank * users
+    mk = lambda *shape, dt=torch.uint8: torch.empty(*shape, dtype=dt, device=dev)  # noqa: E731
+    k_nib, k_qjl, k_nrm = mk(users, H, T, 64), mk(users, H, T, 8), mk(users, H, T, dt=torch.float32)
+    v_nib, v_qjl, v_nrm = mk(users, H, T, 64), mk(users, H, T, 8), mk(users, H, T, dt=torch.float32)
+
+    def step(src_k, src_v):
+        _quantize_into(src_k, cb, ids, True, k_nib, k_qjl, k_nrm, H * T, T, None, 0)
+        _quantize_into(src_v, cb, ids, True, v_nib, v_qjl, v_nrm, H * T, T, None, 0)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        step(xk, xv)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step(xk, xv)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop()
+    tmax = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    ms_step = float(tmax) / args.steps
+    # end to end: new tokens arrive in pinned host memory; a checksum of the norms goes back
+    hk, hv = xk.cpu().pin_memory(), xv.cpu().pin_memory()
+    dk, dv = torch.empty_like(xk), torch.empty_like(xv)
+    e2e_steps = max(1, min(args.steps, 5))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True)
+        step(dk, dv)
+        chk = float(k_nrm.sum().cpu())
+    torch.cuda.synchronize(dev)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e_t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        use_all_host_threads()
+        n = 16
+        xs = xk[:n].cpu()
+        orc.rotate_quantize(xs[:2], cb.cpu(), 0)
+        t0 = time.perf_counter()
+        for u in range(n):
+            orc.rotate_quantize(xs[u:u + 1], cb.cpu(), u)
+        dt = time.perf_counter() - t0
+        cpu = {"value": n * T / dt / 1.0, "unit": "tokens/s", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
+               "kind": "port", "sample": f"{n} users x {H} heads x {T} tokens, K only, CPU oracle (rotate + quantize_heads)"}
+        cpu["value"] = cpu["value"] / 2.0      # a token is a K row and a V row per head
+    if world > 1:
+        dist.barrier(); dist.destroy_process_group()
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peak()
+    rows = 2 * users * H * T
+    alg = rows * (256 + 76)
+    achieved = alg / (ms_step * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "tokens_per_sec_quantize_append", "value": users * T * world / (ms_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "users_per_gpu": users, "kv_heads": H, "new_tokens": T, "rows_per_step": rows,
+                   "l2": "inputs larger than L2" if alg > 2e8 else "inputs smaller than L2"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": peak_kind, "traffic": 321.0 * rows, "algorithmic_bytes_per_launch": alg / 2,
+                     "kernel": "fast_quantize_kernel", "launch_ms": ms_step / 2},
+        "cpu_baseline": cpu,
+        "e2e": {"value": users * T * world / float(e2e_t), "unit": "tokens/s", "h2d_bytes_per_step": 2 * hk.numel() * 2,
+                "d2h_bytes_per_step": 4, "ms_per_step": float(e2e_t) * 1e3},
+        "gpu_launches": 2 * args.steps, "clocks": clocks, "checksum": chk,
+    }))
+
+
 def cpu_baseline(Hq, Hkv, S, lens, budget_s=15.0, n_users=2):
     """Time the CPU oracle (port of the reference's torch path) on ``n_users`` users of the
     workload's shape; repeated until about ``budget_s`` seconds have been spent."""
@@ -348,6 +457,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "append":
+        run_append(args)
     else:
         run_ours(args)
 
