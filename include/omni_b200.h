@@ -136,6 +136,14 @@ int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
                           int32_t n_splits, void* workspace, size_t workspace_bytes,
                           float* out, int32_t* status_word, void* stream);
 
+/* Per-user low-rank query update ahead of attention (kernels/fused_attention.py:166-191 fused prologue,
+ * :401-430 `_apply_lora_to_q`): out[b,h,t,:] = q[b,h,t,:] + alpha * ((x[b,t,:] A[i]^T) B[i]^T)[h,:] with
+ * i = lora_indices[b]; i < 0 copies q unchanged.  x [B][T][hidden], lora_a [n][rank][hidden],
+ * lora_b [n][Hq*128][rank], all fp32 device arrays; q of q_dtype; out fp32 [B][Hq][T][128]; rank <= 128. */
+int32_t omni_lora_q(const void* q, int32_t q_dtype, const float* x, const float* lora_a, const float* lora_b,
+                    const int32_t* lora_indices, float lora_alpha, int64_t B, int32_t Hq, int32_t T,
+                    int32_t hidden, int32_t rank, float* out, void* stream);
+
 /* Allocation-free decode attention.  No counterpart in the reference: it exists for hosts
  * that must not allocate device memory when they call into this library -- an inference
  * server or plugin host that owns the whole device heap and hands its plugins fixed

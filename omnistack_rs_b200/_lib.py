@@ -34,6 +34,7 @@ SIGNATURES = {
     "omni_qattn_decode": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
                                  _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
                                  _vp, _sz, _vp, _vp, _vp]),
+    "omni_lora_q": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _f32, _i64, _i32, _i32, _i32, _i32, _vp, _vp]),
     "omni_qattn_noalloc_scratch_bytes": (_sz, []),
     "omni_qattn_decode_noalloc": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
                                          _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,

@@ -44,17 +44,28 @@ def make_g_matrix(n_kv_heads: int, seed: int, device="cpu"):
 
 def _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha):
     """q[b] += alpha * ((x[b] @ A[idx]^T) @ B[idx]^T) reshaped to heads; idx < 0 leaves the
-    row untouched (reference :401-430).  Batched on the device; returns float32."""
+    row untouched (reference :401-430; the fused prologue :166-191).  Runs ``omni_lora_q``; returns float32."""
     B, Hq, T, D = q.shape
-    idx = lora_indices.to(device=q.device, dtype=torch.long)
-    active = (idx >= 0)
-    safe = idx.clamp(min=0)
-    a = lora_a.to(q.device).float()[safe]                      # (B, rank, hidden)
-    bm = lora_b.to(q.device).float()[safe]                     # (B, Hq*D, rank)
-    down = torch.bmm(x.to(q.device).float(), a.transpose(1, 2))  # (B, T, rank)
-    up = torch.bmm(down, bm.transpose(1, 2))                   # (B, T, Hq*D)
-    delta = up.reshape(B, T, Hq, D).permute(0, 2, 1, 3) * float(lora_alpha)
-    return torch.where(active.view(B, 1, 1, 1), q.float() + delta, q.float())
+    dev = _lib.require_cuda(q)
+    lib = _lib.ensure_init(dev)
+    if q.dtype not in _lib.DTYPE_CODE:
+        raise TypeError(f"unsupported q dtype {q.dtype}")
+    q = q.contiguous()
+    x = x.to(device=dev, dtype=torch.float32).contiguous()
+    la = lora_a.to(device=dev, dtype=torch.float32).contiguous()
+    lb = lora_b.to(device=dev, dtype=torch.float32).contiguous()
+    idx = lora_indices.to(device=dev, dtype=torch.int32).contiguous()
+    rank, hidden = la.shape[1], la.shape[2]
+    if x.shape != (B, T, hidden) or lb.shape[1:] != (Hq * D, rank) or idx.shape != (B,):
+        raise ValueError("LoRA tensors must be x (B,T,hidden), lora_a (n,rank,hidden), lora_b (n,n_heads*128,rank), lora_indices (B,)")
+    if int(idx.max()) >= la.shape[0]:
+        raise IndexError("lora_indices refers to an adapter that does not exist")
+    out = torch.empty(B, Hq, T, D, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.omni_lora_q(_lib.ptr(q), _lib.DTYPE_CODE[q.dtype], _lib.ptr(x), _lib.ptr(la), _lib.ptr(lb),
+                                   _lib.ptr(idx), float(lora_alpha), B, Hq, T, hidden, rank, _lib.ptr(out),
+                                   _lib.stream_ptr(dev)))
+    return out
 
 
 def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int) -> int:

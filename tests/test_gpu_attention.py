@@ -208,3 +208,30 @@ def test_serving_shape_slice_against_oracle(dev):
     vn_const = torch.full_like(vn, 0x77)
     out_c = fa.omni_attn(*to_dev(dev, q, kn, kq, kr, vn_const, cb), user_id=0).cpu()
     assert torch.allclose(out_c, torch.full_like(out_c, float(cb[7])), atol=1e-3)   # fp16 centroids in the tensor-core kernel
+
+
+def test_lora_prologue_shapes_and_batch_consistency(dev):
+    """Per-user LoRA query update (reference tests/unit/test_multi_lora.py: fused vs separate < 1e-3,
+    index -1 reproduces the base output exactly, a user's result does not depend on its batch mates)."""
+    fa = attn_mod()
+    B, Hq, Hkv, T, hid, rank = 5, 8, 2, 2, 96, 8
+    kn, kq, kr, vn, cb, gen = make_cache(B, Hkv, 150, seed=31, user_id=4)
+    q = torch.randn(B, Hq, T, 128, generator=gen).to(torch.bfloat16)
+    x = torch.randn(B, T, hid, generator=gen)
+    la = torch.randn(4, rank, hid, generator=gen) * 0.1
+    lb = torch.randn(4, Hq * 128, rank, generator=gen) * 0.1
+    idx = torch.tensor([3, -1, 0, 0, 2], dtype=torch.int32)
+    q_eff = orc.apply_lora_to_q(q, x, la, lb, idx, 0.7)
+    want = orc.decode_attention(q_eff, kn, kq, kr, vn, cb, 4, 0.09)
+    cache = to_dev(dev, kn, kq, kr, vn, cb)
+    lora = dict(x=x.to(dev), lora_a=la.to(dev), lora_b=lb.to(dev), lora_indices=idx.to(dev), lora_alpha=0.7)
+    out = fa.omni_attn(q.to(dev), *cache, user_id=4, scale=0.09, **lora)
+    assert (out.cpu() - want).abs().max() <= 1e-3
+    base = fa.omni_attn(q.to(dev), *cache, user_id=4, scale=0.09)
+    assert torch.equal(out[1], base[1])
+    solo = fa.omni_attn(q[2:3].to(dev), *[c[2:3] if c.dim() == 4 or c.dim() == 3 else c for c in cache], user_id=4, scale=0.09,
+                        x=x[2:3].to(dev), lora_a=la.to(dev), lora_b=lb.to(dev), lora_indices=idx[2:3].to(dev), lora_alpha=0.7)
+    assert (solo[0] - out[2]).abs().max() <= 1e-4
+    with pytest.raises(IndexError):
+        fa.omni_attn(q.to(dev), *cache, user_id=4, x=x.to(dev), lora_a=la.to(dev), lora_b=lb.to(dev),
+                     lora_indices=torch.full((B,), 9, dtype=torch.int32, device=dev))
