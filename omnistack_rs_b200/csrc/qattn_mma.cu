@@ -590,26 +590,32 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         for (int j = 0; j < nstage; ++j) {
             if (!mbar_wait_bounded(ring.bar0 + 8 * ring.use, ring.use_phase)) { alive = false; break; }
             const uint32_t base = ring.stage0 + ring.use * kStageBytes;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {                       // rows 0-15, then rows 16-31 of the stage
-                const uint32_t bh = base + h * 16 * kNibBytes;
-                kb.ka = lds16(bh + off_k);
-                kb.kb = lds16(bh + off_k + 8 * kNibBytes);
-                kb.v0 = lds8(bh + off_va);
-                kb.v1 = lds8(bh + off_vb);
-                kb.v2 = lds8(bh + off_va + 8 * kNibBytes);
-                kb.v3 = lds8(bh + off_vb + 8 * kNibBytes);
-                if (QJL) {
-                    const AuxRegs& x = h ? aux_b : aux_a;
-                    kb.sa = x.sa; kb.sb = x.sb; kb.na = x.na; kb.nb = x.nb;
-                }
-                if (h == 1 && QJL && j + 1 < nstage) {          // both halves' aux are consumed: fetch the next stage's
+            // both 16-key blocks of the stage are pulled into registers up front, so that the table lookups of the
+            // second block can overlap the softmax of the first
+            KeyBlock kc;
+            kb.ka = lds16(base + off_k);
+            kb.kb = lds16(base + off_k + 8 * kNibBytes);
+            kb.v0 = lds8(base + off_va);
+            kb.v1 = lds8(base + off_vb);
+            kb.v2 = lds8(base + off_va + 8 * kNibBytes);
+            kb.v3 = lds8(base + off_vb + 8 * kNibBytes);
+            kc.ka = lds16(base + 16 * kNibBytes + off_k);
+            kc.kb = lds16(base + 16 * kNibBytes + off_k + 8 * kNibBytes);
+            kc.v0 = lds8(base + 16 * kNibBytes + off_va);
+            kc.v1 = lds8(base + 16 * kNibBytes + off_vb);
+            kc.v2 = lds8(base + 16 * kNibBytes + off_va + 8 * kNibBytes);
+            kc.v3 = lds8(base + 16 * kNibBytes + off_vb + 8 * kNibBytes);
+            if (QJL) {
+                kb.sa = aux_a.sa; kb.sb = aux_a.sb; kb.na = aux_a.na; kb.nb = aux_a.nb;
+                kc.sa = aux_b.sa; kc.sb = aux_b.sb; kc.na = aux_b.na; kc.nb = aux_b.nb;
+                if (j + 1 < nstage) {                          // the next stage's sign bytes and norms
                     ps += kStageKeys * kQjlBytes; pn += kStageKeys;
                     load_aux(aux_a, ps, pn);
                     load_aux(aux_b, ps + 16 * kQjlBytes, pn + 16);
                 }
-                process_key_block<QJL, false>(kb, st, qB, sg, post0, post1, lut_lane, sgn_lane, 16, kr);
             }
+            process_key_block<QJL, false>(kb, st, qB, sg, post0, post1, lut_lane, sgn_lane, 16, kr);
+            process_key_block<QJL, false>(kc, st, qB, sg, post0, post1, lut_lane, sgn_lane, 16, kr);
             // every lane has consumed its bytes of the stage: it can be refilled
             ring_consumed(ring);
             __syncwarp();
