@@ -45,10 +45,10 @@ constexpr int kStages = OMNI_MMA_STAGES;                 // per-warp ring of sta
 constexpr int kStageKeys = 32;                           // keys per stage: two 16-key MMA blocks
 constexpr int kLutSpan = 65536;                          // 256 entries x 256 B
 constexpr int kStageBytes = 2 * kStageKeys * kNibBytes;  // K rows then V rows of one stage
-constexpr int kWarpScratchBytes = 512 + 8 * 64 * 4;      // one fp32 query row + q.g for 8 columns
-// Per-warp private block, 1 KiB aligned (the swizzle pattern of a stage repeats every 512 bytes):
+constexpr int kWarpScratchBytes = 8 * 128 * 4 + 8 * 16;  // fp32 query rows of 8 columns (reused for q.g) + per-column scalars
+// Per-warp private block, 512-byte aligned (the swizzle pattern of a stage repeats every 512 bytes):
 // [kStages stages][scratch][kStages mbarriers][pad]
-constexpr int kWarpBlockBytes = ((kStages * kStageBytes + kWarpScratchBytes + 8 * kStages + 1023) / 1024) * 1024;
+constexpr int kWarpBlockBytes = ((kStages * kStageBytes + kWarpScratchBytes + 8 * kStages + 511) / 512) * 512;
 // Dynamic shared memory: the whole SM.  The tables take the 64 KiB that start at the first 64 KiB
 // boundary of the shared window; the per-warp blocks fill the space in front of and behind them.
 constexpr int kMmaSmemBytes = 227 * 1024;
@@ -128,35 +128,13 @@ __device__ __forceinline__ uint32_t lut_at(uint32_t lut_lane, uint32_t w) {
     asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));   // read-only table: free to be scheduled early
     return v;
 }
-// sign-table lookup: byte WHICH of s = (sign nibble of key row g) | (sign nibble of key row g+8) << 4
-// selects the four A registers of one MMA; sgn_lane has zero bits 8..15
-template <int WHICH>
-__device__ __forceinline__ uint4 sgn_at(uint32_t sgn_lane, uint32_t s) {
-    const uint32_t addr = __byte_perm(s, sgn_lane, 0x7604 | (WHICH << 4));
-    uint4 v;
-    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__host__ __device__ constexpr uint32_t sign_half2(uint32_t bit0, uint32_t bit1) {
-    return 0x3C003C00u ^ (bit0 ? 0u : 0x8000u) ^ (bit1 ? 0u : 0x80000000u);
-}
-
 // ---- QJL correction operands --------------------------------------------------------------
-// Two ways to feed the 64 sign bits of a key to the tensor cores (OMNI_SIGN_INT8 selects):
-//   0: fp16 MMA, A = +-1.0 read from the sign table in shared memory (4 LDS.128 per block);
-//   1: int8 MMA, A = -bit built in registers (multiply spreads 4 bits to the 4 byte MSBs, PRMT
-//      replicates them), B = q.g quantised to int8 per column; no shared-memory traffic.
-#ifndef OMNI_SIGN_INT8
-#define OMNI_SIGN_INT8 1
-#endif
+// The 64 sign bits of a key go to the int8 tensor cores: A = -bit built in registers (a multiply spreads
+// 4 bits to the 4 byte MSBs, PRMT replicates them), B = q.g quantised to int8 per column.
 struct SignB {
-#if OMNI_SIGN_INT8
     uint32_t z[4];          // int8 x4: q.g of column g, projections 16t .. 16t+15
     int zq[4];              // accumulator seed (sum of z)/2 for columns 2t, 2t+1, 2t, 2t+1
     float cs0, cs1;         // -2 * quantisation step of columns 2t, 2t+1
-#else
-    uint32_t g[4][2];       // half2: q.g of column g, projections 16t + 4kk .. +3
-#endif
 };
 __device__ __forceinline__ void imma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1, const int (&c)[4]) {
@@ -171,6 +149,23 @@ __device__ __forceinline__ uint32_t neg_bits_s8(uint32_t s) {
     uint32_t r;
     asm("prmt.b32 %0, %1, %1, 0xBA98;\n" : "=r"(r) : "r"(spread));   // selector MSBs: replicate the byte's sign bit
     return r;                                                  // replicate each MSB
+}
+
+// four int8 of +-1 from 4 bits of a Rademacher row: bit 1 -> +1, bit 0 -> -1 (bits at LOW..LOW+3 of w)
+template <int LOW>
+__device__ __forceinline__ uint32_t pm1_bytes(uint32_t w) {
+    const uint32_t spread = (~w & (0xFu << LOW)) * (LOW == 0 ? 0x10204080u : 0x01020408u);
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %1, 0xBA98;\n" : "=r"(r) : "r"(spread));
+    return r | 0x01010101u;
+}
+__device__ __forceinline__ void imma_acc_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_acc_s8u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // ---- mbarrier / TMA ---------------------------------------------------------------------
@@ -255,7 +250,7 @@ constexpr float kLazyMaxSlack = 6.f;   // log2 units a score may exceed the refe
 template <bool QJL, bool TAIL>
 __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState& st, const uint32_t (&qB)[8][2],
                                                   const SignB& sg, float post0, float post1,
-                                                  uint32_t lut_lane, uint32_t sgn_lane, int nvalid, int kl) {
+                                                  uint32_t lut_lane, int nvalid, int kl) {
     // two independent accumulator chains per product so consecutive MMAs do not wait on each other
     float cd[4], ce[4];
     {
@@ -276,7 +271,6 @@ __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState&
     }
     float s00, s01, s80, s81;           // scores of keys rho(g) / rho(g)+8 for columns 2t / 2t+1, log2 units
     if (QJL) {
-#if OMNI_SIGN_INT8
         // sum_i s_i z_i = -2 * (sum_i (-bit_i) z_i + Z/2): the seed Z/2 rides in as the MMA addend
         const uint32_t sa8 = kb.sa >> 8, sb8 = kb.sb >> 8;
         int d0[4], d1[4];
@@ -288,22 +282,6 @@ __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState&
         s01 = post1 * fmaf(kb.na * sg.cs1, (float)d1[1], cd[1] + ce[1]);
         s80 = post0 * fmaf(kb.nb * sg.cs0, (float)d1[2], cd[2] + ce[2]);
         s81 = post1 * fmaf(kb.nb * sg.cs1, (float)d1[3], cd[3] + ce[3]);
-#else
-        float cq[4], cr[4];
-        // sign groups of the two key rows side by side: byte 0/1 of sx -> bits 0-3 / 8-11, of sy -> bits 4-7 / 12-15
-        const uint32_t sx = (kb.sa & 0x0F0Fu) | ((kb.sb << 4) & 0xF0F0u);
-        const uint32_t sy = ((kb.sa >> 4) & 0x0F0Fu) | (kb.sb & 0xF0F0u);
-        const uint4 q0 = sgn_at<0>(sgn_lane, sx), q1 = sgn_at<0>(sgn_lane, sy);
-        const uint4 q2 = sgn_at<1>(sgn_lane, sx), q3 = sgn_at<1>(sgn_lane, sy);
-        mma_f16_first(cq, q0.x, q0.y, q0.z, q0.w, sg.g[0][0], sg.g[0][1]);
-        mma_f16_first(cr, q1.x, q1.y, q1.z, q1.w, sg.g[1][0], sg.g[1][1]);
-        mma_f16(cq, q2.x, q2.y, q2.z, q2.w, sg.g[2][0], sg.g[2][1]);
-        mma_f16(cr, q3.x, q3.y, q3.z, q3.w, sg.g[3][0], sg.g[3][1]);
-        s00 = post0 * fmaf(kb.na, cq[0] + cr[0], cd[0] + ce[0]);
-        s01 = post1 * fmaf(kb.na, cq[1] + cr[1], cd[1] + ce[1]);
-        s80 = post0 * fmaf(kb.nb, cq[2] + cr[2], cd[2] + ce[2]);
-        s81 = post1 * fmaf(kb.nb, cq[3] + cr[3], cd[3] + ce[3]);
-#endif
     } else {
         s00 = post0 * (cd[0] + ce[0]); s01 = post1 * (cd[1] + ce[1]);
         s80 = post0 * (cd[2] + ce[2]); s81 = post1 * (cd[3] + ce[3]);
@@ -416,19 +394,11 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
             const int byte = i >> 5, ln = i & 31;
             lut[byte * 64 + ln] = pack_half2(__ldg(cb + (byte & 15)), __ldg(cb + (byte >> 4)));
         }
-        if (QJL && !OMNI_SIGN_INT8) {   // sign table in the upper half of every 256-byte slot: 8 copies of 16 bytes
-            for (int i = threadIdx.x; i < 256 * 8; i += blockDim.x) {
-                const uint32_t b = i >> 3, na = b & 15, nb = b >> 4;
-                uint4* dst = reinterpret_cast<uint4*>(smem + lut_off + b * 256 + 128) + (i & 7);
-                *dst = make_uint4(sign_half2(na & 1, na & 2), sign_half2(nb & 1, nb & 2),
-                                  sign_half2(na & 4, na & 8), sign_half2(nb & 4, nb & 8));
-            }
-        }
     }
     const uint32_t lut_lane = smem_base + lut_off + 4 * lane;                  // bits 8..15 are zero
-    const uint32_t sgn_lane = smem_base + lut_off + 128 + 16 * (lane & 7);    // likewise
-    float* qf = reinterpret_cast<float*>(smem + my_off + kStages * kStageBytes);
-    float* qg_s = qf + 128;                                                    // [8][64]
+    float* qrow = reinterpret_cast<float*>(smem + my_off + kStages * kStageBytes);   // [8][128] fp32 query rows ...
+    float* qg_s = qrow;                                                               // ... later [8][64] q.g projections
+    float4* colinfo = reinterpret_cast<float4*>(qrow + 8 * 128);                      // per column: f, post, q.g scale, -
     Ring ring;
     ring.stage0 = smem_base + my_off;
     ring.bar0 = smem_base + my_off + kStages * kStageBytes + kWarpScratchBytes;
@@ -487,98 +457,130 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         }
 
         // ---- prologue: B operands (scaled queries, q.g projections) --------------------------------
-        uint32_t qB[8][2];
-        SignB sg;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) { qB[kk][0] = 0u; qB[kk][1] = 0u; }
-#if OMNI_SIGN_INT8
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) { sg.z[kk] = 0u; sg.zq[kk] = 0; }
-        sg.cs0 = 0.f; sg.cs1 = 0.f;
-#else
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) { sg.g[kk][0] = 0u; sg.g[kk][1] = 0u; }
-#endif
-        float post0 = 1.f, post1 = 1.f;
-        uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0;
-        if (QJL) {
-            const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
-            const uint4* grow = reinterpret_cast<const uint4*>(a.g_rows) + (size_t)seed_of(uid, hkv) * kQjlDim;
-            g0 = __ldg(grow + lane); g1 = __ldg(grow + lane + 32);
-        }
+        // 1. every column's query row goes to shared memory in fp32 together with its scalars
         for (int c = 0; c < ncols; ++c) {
-            const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + c / a.T) * a.T + (c % a.T);
+            const int64_t qrow_idx = (b * a.Hq + (int64_t)hkv * Gq + c / a.T) * a.T + (c % a.T);
             float qv[4];
-            Elem<DT>::load4(a.q, qrow * kHeadDim + 4 * lane, qv);
-            const float mx = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3])))) * fabsf(qs);
-            // keep the fp16 operands below 2^10 in magnitude; the power of two is re-applied to the scores
+            Elem<DT>::load4(a.q, qrow_idx * kHeadDim + 4 * lane, qv);
+            const float amax = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3]))));
+            // fp16 operands stay below 2^10 in magnitude; the power of two is re-applied to the scores
+            const float mx = amax * fabsf(qs);
             float post = 1.f;
             if (mx > 1024.f) post = exp2f(ceilf(log2f(mx * (1.f / 1024.f))));
             const float f = qs / post;
-            __syncwarp();
-            *reinterpret_cast<float4*>(qf + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
-            __syncwarp();
-            if (QJL) {
-                const uint32_t w0[4] = {g0.x, g0.y, g0.z, g0.w}, w1[4] = {g1.x, g1.y, g1.z, g1.w};
-                float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-#pragma unroll 8
-                    for (int j = 0; j < 32; ++j) {
-                        const float qd = qf[w * 32 + j];
-                        acc0 += ((w0[w] >> j) & 1u) ? qd : -qd;
-                        acc1 += ((w1[w] >> j) & 1u) ? qd : -qd;
-                    }
-                }
-                const float q0 = acc0 * (kQjlCoef * f), q1 = acc1 * (kQjlCoef * f);
-#if OMNI_SIGN_INT8
-                // quantise the 64 projections of this column to int8 with one step; keep their sum even
-                const float amax = warp_max(fmaxf(fabsf(q0), fabsf(q1)));
-                const float step = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
-                int z0 = __float2int_rn(q0 / step), z1 = __float2int_rn(q1 / step);
-                int zsum = z0 + z1;
-#pragma unroll
-                for (int m = 16; m >= 1; m >>= 1) zsum += __shfl_xor_sync(kFullMask, zsum, m);
-                if (zsum & 1) {                                   // warp-uniform: zsum and lane 0's value
-                    const int fix = __shfl_sync(kFullMask, z0, 0) < 127 ? 1 : -1;
-                    if (lane == 0) z0 += fix;
-                    zsum += fix;
-                }
-                int8_t* qz = reinterpret_cast<int8_t*>(qg_s);
-                qz[c * 64 + lane] = (int8_t)z0;
-                qz[c * 64 + lane + 32] = (int8_t)z1;
-                if (c == 2 * t)     { sg.zq[0] = zsum / 2; sg.zq[2] = zsum / 2; sg.cs0 = -2.f * step; }
-                if (c == 2 * t + 1) { sg.zq[1] = zsum / 2; sg.zq[3] = zsum / 2; sg.cs1 = -2.f * step; }
-#else
-                qg_s[c * 64 + lane] = q0;
-                qg_s[c * 64 + lane + 32] = q1;
-#endif
-            }
-            if (g == c) {
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const float4 v = *reinterpret_cast<const float4*>(qf + 32 * t + 4 * kk);
-                    qB[kk][0] = pack_half2(v.x * f, v.y * f);
-                    qB[kk][1] = pack_half2(v.z * f, v.w * f);
-                }
-            }
-            if (c == 2 * t) post0 = post;
-            if (c == 2 * t + 1) post1 = post;
+            // int16 fixed point for the q.g projections: amax * sq in [2^14 - 32, 2^15 - 64)
+            const int E = (__float_as_uint(amax) >> 23) & 0xFF;
+            const float sq = (E < 16 || E == 255) ? 0.f : __uint_as_float(((uint32_t)(267 - E) << 23) | 0x7F8000u);
+            *reinterpret_cast<float4*>(qrow + c * 128 + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
+            if (lane == 0) colinfo[c] = make_float4(f, post, sq > 0.f ? kQjlCoef * f / sq : 0.f, sq);
         }
         __syncwarp();
-        if (QJL && g < ncols) {
-#if OMNI_SIGN_INT8
-            const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const int8_t*>(qg_s) + g * 64 + 16 * t);
-            sg.z[0] = v.x; sg.z[1] = v.y; sg.z[2] = v.z; sg.z[3] = v.w;
-#else
+        // 2. thread (g, t) owns column g: its 32 dims d = 32t .. 32t+31 as fp16 (scores) and as int8 limbs (q.g)
+        uint32_t qB[8][2];
+        SignB sg;
+        uint32_t bh[4][2], bl[4][2];
+        if (g < ncols) {
+            const float4 ci = colinfo[g];
+            float qd[32];
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                const float4 v = *reinterpret_cast<const float4*>(qg_s + g * 64 + 16 * t + 4 * kk);
-                sg.g[kk][0] = pack_half2(v.x, v.y);
-                sg.g[kk][1] = pack_half2(v.z, v.w);
+            for (int k = 0; k < 8; ++k) {
+                const float4 v = *reinterpret_cast<const float4*>(qrow + g * 128 + 32 * t + 4 * k);
+                qd[4 * k] = v.x; qd[4 * k + 1] = v.y; qd[4 * k + 2] = v.z; qd[4 * k + 3] = v.w;
+                qB[k][0] = pack_half2(v.x * ci.x, v.y * ci.x);
+                qB[k][1] = pack_half2(v.z * ci.x, v.w * ci.x);
             }
-#endif
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                uint32_t v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(fmaf(qd[8 * ks + k], ci.w, 12582912.f));   // low 16 bits = int16
+                const uint32_t p01 = __byte_perm(v[0], v[1], 0x5140), p23 = __byte_perm(v[2], v[3], 0x5140);
+                const uint32_t p45 = __byte_perm(v[4], v[5], 0x5140), p67 = __byte_perm(v[6], v[7], 0x5140);
+                bl[ks][0] = __byte_perm(p01, p23, 0x5410); bh[ks][0] = __byte_perm(p01, p23, 0x7632);
+                bl[ks][1] = __byte_perm(p45, p67, 0x5410); bh[ks][1] = __byte_perm(p45, p67, 0x7632);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { qB[k][0] = 0u; qB[k][1] = 0u; }
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) { bl[ks][0] = 0u; bl[ks][1] = 0u; bh[ks][0] = 0u; bh[ks][1] = 0u; }
         }
+        float post0 = 1.f, post1 = 1.f;
+        if (2 * t < ncols) post0 = colinfo[2 * t].y;
+        if (2 * t + 1 < ncols) post1 = colinfo[2 * t + 1].y;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { sg.z[k] = 0u; sg.zq[k] = 0; }
+        sg.cs0 = 0.f; sg.cs1 = 0.f;
+        if (QJL) {
+            // 3. q.g for all columns on the int8 tensor cores: A = G (+-1, built from the bit rows), B = the limbs;
+            //    MMA k index 4t'+j / 16+4t'+j  <->  d = 32t' + 8ks + j / + 4 + j
+            const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
+            const uint32_t* grow = a.g_rows + (size_t)seed_of(uid, hkv) * kQjlDim * 4;
+            const float inv0 = (2 * t < ncols) ? colinfo[2 * t].z : 0.f, inv1 = (2 * t + 1 < ncols) ? colinfo[2 * t + 1].z : 0.f;
+            __syncwarp();                                            // all reads of the query rows are done
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                const uint32_t w0 = __ldg(grow + (16 * mt + g) * 4 + t), w1 = __ldg(grow + (16 * mt + g + 8) * 4 + t);
+                int chi[4] = {0, 0, 0, 0}, clo[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint32_t x0 = w0 >> (8 * ks), x1 = w1 >> (8 * ks);
+                    const uint32_t a0 = pm1_bytes<0>(x0), a1 = pm1_bytes<0>(x1), a2 = pm1_bytes<4>(x0), a3 = pm1_bytes<4>(x1);
+                    imma_acc_s8s8(chi, a0, a1, a2, a3, bh[ks][0], bh[ks][1]);
+                    imma_acc_s8u8(clo, a0, a1, a2, a3, bl[ks][0], bl[ks][1]);
+                }
+                // C element j: projection 16mt + g + 8(j>>1), column 2t + (j&1)
+                if (2 * t < ncols) {
+                    qg_s[(2 * t) * 64 + 16 * mt + g] = (float)(chi[0] * 256 + clo[0]) * inv0;
+                    qg_s[(2 * t) * 64 + 16 * mt + g + 8] = (float)(chi[2] * 256 + clo[2]) * inv0;
+                }
+                if (2 * t + 1 < ncols) {
+                    qg_s[(2 * t + 1) * 64 + 16 * mt + g] = (float)(chi[1] * 256 + clo[1]) * inv1;
+                    qg_s[(2 * t + 1) * 64 + 16 * mt + g + 8] = (float)(chi[3] * 256 + clo[3]) * inv1;
+                }
+            }
+            __syncwarp();
+            // 4. quantise column g's 64 projections to int8 with one step; keep their sum even (it is halved)
+            //    (every lane runs the shuffles; lanes of unused columns work on zeros)
+            const bool mine = g < ncols;
+            float v[16];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (mine) x = *reinterpret_cast<const float4*>(qg_s + g * 64 + 16 * t + 4 * k);
+                v[4 * k] = x.x; v[4 * k + 1] = x.y; v[4 * k + 2] = x.z; v[4 * k + 3] = x.w;
+            }
+            float am = 0.f;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) am = fmaxf(am, fabsf(v[k]));
+            am = fmaxf(am, __shfl_xor_sync(kFullMask, am, 1));
+            am = fmaxf(am, __shfl_xor_sync(kFullMask, am, 2));
+            const float step = am > 0.f ? am * (1.f / 127.f) : 1.f, rstep = 1.f / step;
+            int z[16], zsum = 0;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) { z[k] = __float2int_rn(v[k] * rstep); zsum += z[k]; }
+            zsum += __shfl_xor_sync(kFullMask, zsum, 1);
+            zsum += __shfl_xor_sync(kFullMask, zsum, 2);
+            const int z_first = __shfl_sync(kFullMask, z[0], lane & ~3);     // the column's first projection (lane t = 0)
+            if (zsum & 1) {                                                  // uniform over the column's four lanes
+                const int fix = z_first < 127 ? 1 : -1;
+                if (t == 0) z[0] += fix;
+                zsum += fix;
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t p01 = __byte_perm(z[4 * k], z[4 * k + 1], 0x5140), p23 = __byte_perm(z[4 * k + 2], z[4 * k + 3], 0x5140);
+                sg.z[k] = __byte_perm(p01, p23, 0x5410);
+            }
+            const float mycs = mine ? -2.f * step : 0.f;
+            const int myzh = zsum / 2;
+            // the thread's score columns are 2t and 2t+1: fetch their seeds and steps from those columns' lanes
+            sg.zq[0] = sg.zq[2] = __shfl_sync(kFullMask, myzh, 8 * t);
+            sg.zq[1] = sg.zq[3] = __shfl_sync(kFullMask, myzh, 8 * t + 4);
+            sg.cs0 = __shfl_sync(kFullMask, mycs, 8 * t);
+            sg.cs1 = __shfl_sync(kFullMask, mycs, 8 * t + 4);
+        }
+        __syncwarp();
 
         WarpState st;
 #pragma unroll
@@ -614,8 +616,8 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
                     load_aux(aux_b, ps + 16 * kQjlBytes, pn + 16);
                 }
             }
-            process_key_block<QJL, false>(kb, st, qB, sg, post0, post1, lut_lane, sgn_lane, 16, kr);
-            process_key_block<QJL, false>(kc, st, qB, sg, post0, post1, lut_lane, sgn_lane, 16, kr);
+            process_key_block<QJL, false>(kb, st, qB, sg, post0, post1, lut_lane, 16, kr);
+            process_key_block<QJL, false>(kc, st, qB, sg, post0, post1, lut_lane, 16, kr);
             // every lane has consumed its bytes of the stage: it can be refilled
             ring_consumed(ring);
             __syncwarp();
@@ -625,7 +627,7 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         for (int k0 = nstage * kStageKeys; k0 < nkeys; k0 += 16) {     // up to two blocks with plain clamped loads
             const int nvalid = nkeys - k0 < 16 ? nkeys - k0 : 16;
             load_tail_block<QJL>(kb, a, row0 + k0, nvalid, kr, va, vb, g, t);
-            process_key_block<QJL, true>(kb, st, qB, sg, post0, post1, lut_lane, sgn_lane, nvalid, kr);
+            process_key_block<QJL, true>(kb, st, qB, sg, post0, post1, lut_lane, nvalid, kr);
         }
 
         // ---- epilogue ----------------------------------------------------------------------
