@@ -44,6 +44,10 @@ extern "C" {
 #define OMNI_ERR_DEVICE_WAIT  4   /* a bounded device-side wait expired (status word non-zero)  */
 #define OMNI_ERR_NOT_INIT     5   /* omni_init() has not been called for the current device     */
 
+/* values a kernel may leave in a caller's device status word (0 = nothing to report) */
+#define OMNI_STATUS_WAIT_EXPIRED  4   /* a bounded device-side wait ran out                      */
+#define OMNI_STATUS_BAD_INDEX     7   /* an adapter index was at or past the adapter count       */
+
 /* element types of floating-point inputs */
 #define OMNI_F32   0
 #define OMNI_BF16  1
@@ -139,10 +143,40 @@ int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
 /* Per-user low-rank query update ahead of attention (kernels/fused_attention.py:166-191 fused prologue,
  * :401-430 `_apply_lora_to_q`): out[b,h,t,:] = q[b,h,t,:] + alpha * ((x[b,t,:] A[i]^T) B[i]^T)[h,:] with
  * i = lora_indices[b]; i < 0 copies q unchanged.  x [B][T][hidden], lora_a [n][rank][hidden],
- * lora_b [n][Hq*128][rank], all fp32 device arrays; q of q_dtype; out fp32 [B][Hq][T][128]; rank <= 128. */
+ * lora_b [n][Hq*128][rank], all fp32 device arrays; q of q_dtype; out fp32 [B][Hq][T][128]; rank <= 128.
+ * n_adapters = n: a row whose index is >= n is copied unchanged and `status_word` (device int32 or NULL) is
+ * raised to OMNI_STATUS_BAD_INDEX (the reference's gather would fail there); no host-side check, no sync. */
 int32_t omni_lora_q(const void* q, int32_t q_dtype, const float* x, const float* lora_a, const float* lora_b,
-                    const int32_t* lora_indices, float lora_alpha, int64_t B, int32_t Hq, int32_t T,
-                    int32_t hidden, int32_t rank, float* out, void* stream);
+                    const int32_t* lora_indices, int32_t n_adapters, float lora_alpha, int64_t B, int32_t Hq,
+                    int32_t T, int32_t hidden, int32_t rank, float* out, int32_t* status_word, void* stream);
+
+/* Attention with the per-user low-rank query update in the same call (the reference passes x, lora_a, lora_b,
+ * lora_indices and lora_alpha to `omni_attn`, kernels/fused_attention.py:537-560, and applies them in the
+ * kernel prologue :166-191).  `lora` == NULL makes this omni_qattn_decode.  Otherwise the update runs first on
+ * the same stream into the front of `workspace`, which must hold omni_qattn_lora_workspace_bytes(...) bytes
+ * (the updated fp32 queries, then the split-K partial states); q may be of any q_dtype.                      */
+typedef struct omni_lora {
+    const float*   x;             /* device fp32 [B][T][hidden]                 */
+    const float*   lora_a;        /* device fp32 [n_adapters][rank][hidden]     */
+    const float*   lora_b;        /* device fp32 [n_adapters][Hq*128][rank]     */
+    const int32_t* lora_indices;  /* device int32 [B]; < 0 = no adapter         */
+    int32_t        n_adapters;
+    int32_t        hidden;
+    int32_t        rank;          /* <= 128                                     */
+    float          alpha;
+} omni_lora_t;
+size_t  omni_qattn_lora_workspace_bytes(int64_t B, int32_t Hq, int32_t T, int32_t n_splits);
+int32_t omni_qattn_decode_lora(const void* q, int32_t q_dtype,
+                               const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
+                               const uint8_t* v_nib,
+                               const float* codebooks, int32_t cb_per_head,
+                               const int32_t* user_ids, int32_t user_id,
+                               const int32_t* seq_lens, const int32_t* cache_slots,
+                               int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
+                               int64_t ks_b, int64_t ks_h,
+                               float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out,
+                               int32_t n_splits, void* workspace, size_t workspace_bytes,
+                               float* out, int32_t* status_word, void* stream, const omni_lora_t* lora);
 
 /* Allocation-free decode attention.  No counterpart in the reference: it exists for hosts
  * that must not allocate device memory when they call into this library -- an inference

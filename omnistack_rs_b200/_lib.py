@@ -5,6 +5,7 @@ or a tensor is not on a CUDA device, the call raises.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 import os
 import threading
@@ -34,7 +35,11 @@ SIGNATURES = {
     "omni_qattn_decode": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
                                  _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
                                  _vp, _sz, _vp, _vp, _vp]),
-    "omni_lora_q": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _f32, _i64, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "omni_lora_q": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _f32, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "omni_qattn_lora_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32]),
+    "omni_qattn_decode_lora": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
+                                      _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
+                                      _vp, _sz, _vp, _vp, _vp, _vp]),
     "omni_qattn_noalloc_scratch_bytes": (_sz, []),
     "omni_qattn_decode_noalloc": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
                                          _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
@@ -112,12 +117,38 @@ def ensure_init(device: torch.device) -> C.CDLL:
     return lib
 
 
+class OmniLora(C.Structure):
+    """``omni_lora_t`` of the C header."""
+    _fields_ = [("x", C.c_void_p), ("lora_a", C.c_void_p), ("lora_b", C.c_void_p), ("lora_indices", C.c_void_p),
+                ("n_adapters", C.c_int32), ("hidden", C.c_int32), ("rank", C.c_int32), ("alpha", C.c_float)]
+
+
+_NULL_CONTEXT = contextlib.nullcontext()
+
+
+def on_device(device: torch.device):
+    """Context manager that makes ``device`` current (free when it already is)."""
+    if device.index is None or torch.cuda.current_device() == device.index:
+        return _NULL_CONTEXT
+    return torch.cuda.device(device)
+
+
 def ptr(x):
-    return None if x is None else C.c_void_p(x.data_ptr())
+    """Address of a tensor's storage as ctypes takes it for a ``void*`` argument (None = NULL)."""
+    return None if x is None else x.data_ptr()
 
 
 def stream_ptr(device: torch.device):
-    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    """Raw handle of torch's current stream on ``device``."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return torch._C._cuda_getCurrentRawStream(idx) or None
+
+
+def as_device(x: torch.Tensor, device: torch.device, dtype: torch.dtype) -> torch.Tensor:
+    """``x`` as a contiguous tensor of ``dtype`` on ``device``; ``x`` itself when it already is one."""
+    if x.dtype is dtype and x.device == device and x.is_contiguous():
+        return x
+    return x.to(device=device, dtype=dtype).contiguous()
 
 
 _status_words = {}
@@ -132,10 +163,13 @@ def status_word(device: torch.device) -> torch.Tensor:
 
 
 def check_device_status(device: torch.device) -> None:
-    """Synchronises the device and raises if a kernel reported an expired wait since the last check."""
+    """Synchronises the device and raises if a kernel reported an expired wait (RuntimeError) or an
+    adapter index past the adapter count (IndexError) since the last check."""
     w = status_word(device)
     torch.cuda.synchronize(device)
     code = int(w.item())
     if code != 0:
         w.zero_()
+        if code == 7:
+            raise IndexError("omni_b200: lora_indices refers to an adapter that does not exist")
         raise RuntimeError(f"omni_b200: a device-side bounded wait expired (status {code})")

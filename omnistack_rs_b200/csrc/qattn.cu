@@ -235,7 +235,10 @@ static KernelChoice kernel_choice_from_env() {
 static int32_t launch(const AttnArgs& a, cudaStream_t st) {
     if (a.B == 0 || a.T == 0) return OMNI_OK;
     const KernelChoice choice = kernel_choice_from_env();
-    const bool use_mma = mma_eligible(a) && (choice == kMma || (choice == kAuto && a.S >= 128));
+    // measured crossover: the tensor-core kernel wins from 128 keys on, and for shorter caches once the
+    // lane-per-key kernel would need more than about a thousand warps
+    const bool use_mma = mma_eligible(a) &&
+                         (choice == kMma || (choice == kAuto && (a.S >= 128 || a.B * a.Hq * a.T >= 1024)));
     if (use_mma) {
         const int32_t rc = launch_mma(a, st);
         if (rc != OMNI_OK) return rc;
@@ -324,6 +327,48 @@ extern "C" int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
                cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
                (float*)workspace, out, tb->rows, status_word};
     int32_t st = validate(a, workspace_bytes);
+    if (st != OMNI_OK) return st;
+    return launch(a, (cudaStream_t)stream);
+}
+
+static size_t lora_q_bytes(int64_t B, int32_t Hq, int32_t T) {
+    if (B <= 0 || Hq <= 0 || T <= 0) return 0;
+    return (((size_t)B * Hq * T * kHeadDim * sizeof(float)) + 255) & ~(size_t)255;
+}
+
+extern "C" size_t omni_qattn_lora_workspace_bytes(int64_t B, int32_t Hq, int32_t T, int32_t n_splits) {
+    return lora_q_bytes(B, Hq, T) + omni_qattn_workspace_bytes(B, Hq, T, n_splits);
+}
+
+extern "C" int32_t omni_qattn_decode_lora(const void* q, int32_t q_dtype,
+                                          const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
+                                          const uint8_t* v_nib, const float* codebooks, int32_t cb_per_head,
+                                          const int32_t* user_ids, int32_t user_id,
+                                          const int32_t* seq_lens, const int32_t* cache_slots,
+                                          int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
+                                          int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
+                                          int32_t rotate_q, int32_t unrotate_out, int32_t n_splits,
+                                          void* workspace, size_t workspace_bytes, float* out,
+                                          int32_t* status_word, void* stream, const omni_lora_t* lora) {
+    if (!lora)
+        return omni_qattn_decode(q, q_dtype, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id,
+                                 seq_lens, cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q,
+                                 unrotate_out, n_splits, workspace, workspace_bytes, out, status_word, stream);
+    const DeviceTables* tb = tables_for_current_device();
+    if (!tb) return OMNI_ERR_NOT_INIT;
+    const size_t qb = lora_q_bytes(B, Hq, T);
+    OMNI_REQUIRE(B == 0 || T == 0 || (workspace && workspace_bytes >= qb), OMNI_ERR_ARG,
+                 "qattn_decode_lora: the workspace must hold omni_qattn_lora_workspace_bytes(...) = %zu bytes, got %zu",
+                 omni_qattn_lora_workspace_bytes(B, Hq, T, n_splits), workspace_bytes);
+    float* q_eff = (float*)workspace;
+    AttnArgs a{q_eff, OMNI_F32, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id, seq_lens,
+               cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
+               (float*)((char*)workspace + qb), out, tb->rows, status_word};
+    int32_t st = validate(a, workspace_bytes - (B == 0 || T == 0 ? 0 : qb));
+    if (st != OMNI_OK) return st;
+    OMNI_REQUIRE(q, OMNI_ERR_ARG, "qattn_decode_lora: NULL q");
+    st = omni_lora_q(q, q_dtype, lora->x, lora->lora_a, lora->lora_b, lora->lora_indices, lora->n_adapters, lora->alpha,
+                     B, Hq, T, lora->hidden, lora->rank, q_eff, status_word, stream);
     if (st != OMNI_OK) return st;
     return launch(a, (cudaStream_t)stream);
 }

@@ -31,6 +31,8 @@
 #include "qattn.cuh"
 #include <cuda.h>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 namespace omni {
 
@@ -716,11 +718,39 @@ bool mma_eligible(const AttnArgs& a) {
     return cols <= 8 && !a.rotate_q && !a.unrotate_out && a.Hkv <= 65535;
 }
 
+// Per-device facts that never change while the process lives: looked up once, then read without a driver call.
+static int g_sm_count[kMaxDevices];          // 0 = not yet queried
+static std::mutex g_once_mutex;
+
+static int32_t sm_count_of(int dev, int* sms) {
+    if (dev < 0 || dev >= kMaxDevices) {
+        OMNI_CUDA(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+        return OMNI_OK;
+    }
+    std::lock_guard<std::mutex> lk(g_once_mutex);
+    if (g_sm_count[dev] == 0) OMNI_CUDA(cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
+    *sms = g_sm_count[dev];
+    return OMNI_OK;
+}
+
+// The opt-in to the full shared-memory carve-out is per kernel and per device; it is made once for each pair.
+// (All instantiations of the kernel share one function-pointer type, so the record is keyed by address.)
+static int32_t allow_full_smem(const void* kern, int dev) {
+    static std::vector<std::pair<const void*, int>> done;
+    std::lock_guard<std::mutex> lk(g_once_mutex);
+    for (const auto& p : done)
+        if (p.first == kern && p.second == dev) return OMNI_OK;
+    OMNI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemBytes));
+    done.emplace_back(kern, dev);
+    return OMNI_OK;
+}
+
 template <int DT>
 static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     int dev = 0, sms = 148;
     OMNI_CUDA(cudaGetDevice(&dev));
-    OMNI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int32_t rc = sm_count_of(dev, &sms);
+    if (rc != OMNI_OK) return rc;
     // Persistent CTAs, one per SM.  With one shared codebook a CTA serves every kv head
     // (grid.y == 1, the head is part of the item index); with per-head codebooks a CTA is
     // bound to one head because its lookup table is built from that head's centroids.
@@ -739,12 +769,17 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     if (ctas > need) ctas = need;
     dim3 grid((unsigned)ctas, gy);
     CUtensorMap map_k, map_v;
-    int32_t rc = make_nibble_map(&map_k, a.k_nib);
+    rc = make_nibble_map(&map_k, a.k_nib);
     if (rc != OMNI_OK) return rc;
-    rc = make_nibble_map(&map_v, a.v_nib);
-    if (rc != OMNI_OK) return rc;
+    if (a.v_nib == a.k_nib) {
+        map_v = map_k;
+    } else {
+        rc = make_nibble_map(&map_v, a.v_nib);
+        if (rc != OMNI_OK) return rc;
+    }
     auto kern = a.with_qjl ? qattn_mma_kernel<DT, true> : qattn_mma_kernel<DT, false>;
-    OMNI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemBytes));
+    rc = allow_full_smem(reinterpret_cast<const void*>(kern), dev);
+    if (rc != OMNI_OK) return rc;
     kern<<<grid, kMmaWarps * 32, kMmaSmemBytes, st>>>(a, items, map_k, map_v);
     return check_cuda(cudaGetLastError(), "qattn_mma_kernel launch");
 }

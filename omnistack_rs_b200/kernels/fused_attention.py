@@ -17,6 +17,7 @@ Additive keyword arguments: ``seq_lens`` (per-user valid length), ``rotate_q`` /
 """
 from __future__ import annotations
 
+import ctypes as C
 import math
 from typing import Optional
 
@@ -42,9 +43,26 @@ def make_g_matrix(n_kv_heads: int, seed: int, device="cpu"):
     return g_lo.to(device), g_hi.to(device)
 
 
+def _prep_lora(q, x, lora_a, lora_b, lora_indices, dev):
+    """Validated fp32 / int32 device tensors of the per-user query update."""
+    B, Hq, T, D = q.shape
+    if lora_indices.device.type == "cpu" and lora_indices.numel() and int(lora_indices.max()) >= lora_a.shape[0]:
+        raise IndexError("lora_indices refers to an adapter that does not exist")
+    x = _lib.as_device(x, dev, torch.float32)
+    la = _lib.as_device(lora_a, dev, torch.float32)
+    lb = _lib.as_device(lora_b, dev, torch.float32)
+    idx = _lib.as_device(lora_indices, dev, torch.int32)
+    rank, hidden = la.shape[1], la.shape[2]
+    if x.shape != (B, T, hidden) or lb.shape[1:] != (Hq * D, rank) or idx.shape != (B,):
+        raise ValueError("LoRA tensors must be x (B,T,hidden), lora_a (n,rank,hidden), lora_b (n,n_heads*128,rank), lora_indices (B,)")
+    return x, la, lb, idx
+
+
 def _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha):
     """q[b] += alpha * ((x[b] @ A[idx]^T) @ B[idx]^T) reshaped to heads; idx < 0 leaves the
-    row untouched (reference :401-430; the fused prologue :166-191).  Runs ``omni_lora_q``; returns float32."""
+    row untouched (reference :401-430; the fused prologue :166-191).  Runs ``omni_lora_q``; returns float32.
+    Indices held on the host are range-checked here; indices already on the device are checked by the kernel,
+    which reports through the device status word (``_lib.check_device_status`` raises ``IndexError``)."""
     B, Hq, T, D = q.shape
     dev = _lib.require_cuda(q)
     lib = _lib.ensure_init(dev)
@@ -54,17 +72,17 @@ def _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha):
     x = x.to(device=dev, dtype=torch.float32).contiguous()
     la = lora_a.to(device=dev, dtype=torch.float32).contiguous()
     lb = lora_b.to(device=dev, dtype=torch.float32).contiguous()
+    if lora_indices.device.type == "cpu" and lora_indices.numel() and int(lora_indices.max()) >= lora_a.shape[0]:
+        raise IndexError("lora_indices refers to an adapter that does not exist")
     idx = lora_indices.to(device=dev, dtype=torch.int32).contiguous()
     rank, hidden = la.shape[1], la.shape[2]
     if x.shape != (B, T, hidden) or lb.shape[1:] != (Hq * D, rank) or idx.shape != (B,):
         raise ValueError("LoRA tensors must be x (B,T,hidden), lora_a (n,rank,hidden), lora_b (n,n_heads*128,rank), lora_indices (B,)")
-    if int(idx.max()) >= la.shape[0]:
-        raise IndexError("lora_indices refers to an adapter that does not exist")
     out = torch.empty(B, Hq, T, D, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         _lib.check(lib.omni_lora_q(_lib.ptr(q), _lib.DTYPE_CODE[q.dtype], _lib.ptr(x), _lib.ptr(la), _lib.ptr(lb),
-                                   _lib.ptr(idx), float(lora_alpha), B, Hq, T, hidden, rank, _lib.ptr(out),
-                                   _lib.stream_ptr(dev)))
+                                   _lib.ptr(idx), la.shape[0], float(lora_alpha), B, Hq, T, hidden, rank, _lib.ptr(out),
+                                   _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
     return out
 
 
@@ -82,7 +100,8 @@ def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int) -> int:
 
 
 def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
-           seq_lens=None, cache_slots=None, rotate_q=False, unrotate_out=False, n_splits=None):
+           seq_lens=None, cache_slots=None, rotate_q=False, unrotate_out=False, n_splits=None, lora=None):
+    """One call of ``omni_qattn_decode_lora``; ``lora`` = (x, lora_a, lora_b, lora_indices, lora_alpha) or None."""
     dev = _lib.require_cuda(q, k_nibbles, k_qjl, k_norms, v_nibbles)
     lib = _lib.ensure_init(dev)
     B, Hq, T, D = q.shape
@@ -97,25 +116,31 @@ def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, w
         raise TypeError(f"unsupported q dtype {q.dtype}")
     q = q.contiguous()
     k_nibbles, k_qjl, v_nibbles = k_nibbles.contiguous(), k_qjl.contiguous(), v_nibbles.contiguous()
-    k_norms = k_norms.contiguous().float()
+    k_norms = _lib.as_device(k_norms, dev, torch.float32)
     cb, per_head = _prep_codebooks(codebooks, Hkv, dev)
     ids, uid = _user_args(user_id, B, dev)
-    lens = None if seq_lens is None else seq_lens.to(device=dev, dtype=torch.int32).contiguous()
-    slots = None if cache_slots is None else cache_slots.to(device=dev, dtype=torch.int32).contiguous()
+    lens = None if seq_lens is None else _lib.as_device(seq_lens, dev, torch.int32)
+    slots = None if cache_slots is None else _lib.as_device(cache_slots, dev, torch.int32)
     if n_splits is None:
         n_splits = _auto_splits(B, Hq, Hkv, T, S)
-    ws, ws_bytes = None, 0
-    if n_splits > 1:
+    ws, ws_bytes, lora_arg = None, 0, None
+    if lora is not None:
+        x, la, lb, idx = _prep_lora(q, lora[0], lora[1], lora[2], lora[3], dev)
+        lora_arg = C.byref(_lib.OmniLora(x.data_ptr(), la.data_ptr(), lb.data_ptr(), idx.data_ptr(), la.shape[0],
+                                         la.shape[2], la.shape[1], float(lora[4])))
+        ws_bytes = lib.omni_qattn_lora_workspace_bytes(B, Hq, T, n_splits)
+    elif n_splits > 1:
         ws_bytes = lib.omni_qattn_workspace_bytes(B, Hq, T, n_splits)
+    if ws_bytes:
         ws = torch.empty(ws_bytes // 4, dtype=torch.float32, device=dev)
     out = torch.empty(B, Hq, T, HEAD_DIM, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
-        _lib.check(lib.omni_qattn_decode(
+    with _lib.on_device(dev):
+        _lib.check(lib.omni_qattn_decode_lora(
             _lib.ptr(q), _lib.DTYPE_CODE[q.dtype], _lib.ptr(k_nibbles), _lib.ptr(k_qjl), _lib.ptr(k_norms),
             _lib.ptr(v_nibbles), _lib.ptr(cb), per_head, _lib.ptr(ids), uid, _lib.ptr(lens), _lib.ptr(slots),
             B, Hq, Hkv, T, S, Hkv * S, S, float(scale), int(bool(with_qjl)), int(bool(rotate_q)),
             int(bool(unrotate_out)), int(n_splits), _lib.ptr(ws), ws_bytes, _lib.ptr(out), _lib.ptr(_lib.status_word(dev)),
-            _lib.stream_ptr(dev)))
+            _lib.stream_ptr(dev), lora_arg))
     return out
 
 
@@ -128,8 +153,8 @@ class OmniAttention(torch.autograd.Function):
                 g_matrix=None, x=None, lora_a=None, lora_b=None, lora_indices=None, lora_alpha=1.0):
         if scale is None:
             scale = 1.0 / math.sqrt(HEAD_DIM)
-        q_eff = q if x is None else _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha)
-        out = _qattn(q_eff, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl)
+        lora = None if x is None else (x, lora_a, lora_b, lora_indices, lora_alpha)
+        out = _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl, lora=lora)
         ctx.save_for_backward(q, out)
         ctx.scale, ctx.with_qjl = scale, with_qjl
         return out
@@ -144,11 +169,12 @@ def omni_attn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id=0, sca
               lora_alpha: float = 1.0, *, seq_lens=None, cache_slots=None, rotate_q: bool = False,
               unrotate_out: bool = False, n_splits: Optional[int] = None) -> torch.Tensor:
     """Fused INT4 + QJL attention with the optional per-user LoRA query update."""
-    if seq_lens is None and cache_slots is None and not rotate_q and not unrotate_out and n_splits is None:
+    plain = seq_lens is None and cache_slots is None and not rotate_q and not unrotate_out and n_splits is None
+    if plain and torch.is_grad_enabled() and q.requires_grad:          # only then does the autograd node matter
         return OmniAttention.apply(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
                                    g_matrix, x, lora_a, lora_b, lora_indices, lora_alpha)
     if scale is None:
         scale = 1.0 / math.sqrt(HEAD_DIM)
-    q_eff = q if x is None else _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha)
-    return _qattn(q_eff, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
-                  seq_lens, cache_slots, rotate_q, unrotate_out, n_splits)
+    lora = None if x is None else (x, lora_a, lora_b, lora_indices, lora_alpha)
+    return _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
+                  seq_lens, cache_slots, rotate_q, unrotate_out, n_splits, lora)

@@ -33,7 +33,7 @@ def _prep_codebooks(codebooks: torch.Tensor, n_heads: int, dev) -> Tuple[torch.T
         assert codebooks.shape == (n_heads, 16), codebooks.shape
     else:
         assert codebooks.shape == (16,), codebooks.shape
-    return codebooks.to(device=dev, dtype=torch.float32).contiguous(), int(per_head)
+    return _lib.as_device(codebooks, dev, torch.float32), int(per_head)
 
 
 def _user_args(user_id: Union[int, torch.Tensor], B: int, dev):

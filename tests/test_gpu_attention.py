@@ -229,9 +229,21 @@ def test_lora_prologue_shapes_and_batch_consistency(dev):
     assert (out.cpu() - want).abs().max() <= 1e-3
     base = fa.omni_attn(q.to(dev), *cache, user_id=4, scale=0.09)
     assert torch.equal(out[1], base[1])
+    # the one-call entry point (update, then attention, split-K on) equals the two separate calls bit for bit
+    two_step = fa._qattn(fa._apply_lora_to_q(q.to(dev), **lora), *cache, 4, 0.09, True, n_splits=3)
+    one_call = fa.omni_attn(q.to(dev), *cache, user_id=4, scale=0.09, n_splits=3, **lora)
+    assert torch.equal(one_call, two_step)
+    assert (one_call.cpu() - want).abs().max() <= 1e-3
     solo = fa.omni_attn(q[2:3].to(dev), *[c[2:3] if c.dim() == 4 or c.dim() == 3 else c for c in cache], user_id=4, scale=0.09,
                         x=x[2:3].to(dev), lora_a=la.to(dev), lora_b=lb.to(dev), lora_indices=idx[2:3].to(dev), lora_alpha=0.7)
     assert (solo[0] - out[2]).abs().max() <= 1e-4
-    with pytest.raises(IndexError):
+    from omnistack_rs_b200 import _lib
+    with pytest.raises(IndexError):                       # host-resident indices: checked before the launch
         fa.omni_attn(q.to(dev), *cache, user_id=4, x=x.to(dev), lora_a=la.to(dev), lora_b=lb.to(dev),
-                     lora_indices=torch.full((B,), 9, dtype=torch.int32, device=dev))
+                     lora_indices=torch.full((B,), 9, dtype=torch.int32))
+    with pytest.raises(IndexError):                       # device-resident indices: reported through the status word
+        bad = fa.omni_attn(q.to(dev), *cache, user_id=4, scale=0.09, x=x.to(dev), lora_a=la.to(dev), lora_b=lb.to(dev),
+                           lora_indices=torch.full((B,), 9, dtype=torch.int32, device=dev), lora_alpha=0.7)
+        _lib.check_device_status(dev)
+    plain = fa.omni_attn(q.to(dev), *cache, user_id=4, scale=0.09)
+    assert torch.equal(bad, plain)                        # such rows keep q unchanged
