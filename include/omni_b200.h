@@ -101,6 +101,20 @@ int32_t omni_dequantize_heads(const uint8_t* nib, const uint8_t* qjl, const floa
                               int64_t is_b, int64_t is_h, int32_t with_qjl,
                               float* out, void* stream);
 
+/* Lloyd-Max fit of 16-level codebooks (quantization/codebook.py:64-108 `LloydMaxCalibrator.fit`, :148-172
+ * `calibrate_per_group`): equal-mass initialisation, first-index nearest-centroid assignment in fp32, mean
+ * update (an empty cell keeps its centroid), stop once the largest move is below `tol` or after `max_iters`
+ * iterations, ascending output.  `sorted` holds the fp32 samples of all groups back to back on the device, each
+ * group in ASCENDING order; group g is sorted[group_offsets[g] .. group_offsets[g+1]) (device int64
+ * [n_groups+1], first entry 0, last n_total, at least 16 samples per group).  `workspace`: device scratch of
+ * omni_lloyd_max_workspace_bytes(n_total) bytes (fp64 prefix sums).  codebooks: device fp32 [n_groups][16];
+ * iters_out: device int32 [n_groups] (iterations run) or NULL.  Means are formed in fp64 and rounded once, so
+ * the result equals the reference's to a few fp32 ulps rather than bit for bit.                                */
+size_t  omni_lloyd_max_workspace_bytes(int64_t n_total);
+int32_t omni_lloyd_max_fit(const float* sorted, int64_t n_total, const int64_t* group_offsets, int32_t n_groups,
+                           int32_t max_iters, double tol, void* workspace, size_t workspace_bytes,
+                           float* codebooks, int32_t* iters_out, void* stream);
+
 /* Row-seeded codec (kernels/quantize.py:456-499 `quantize_rows`, :502-537
  * `dequantize_rows`): row i of n_rows contiguous fp32 rows uses seed
  * (user_id mod 1024) xor (base_head_idx + i).  One shared [16] codebook. */
