@@ -240,7 +240,10 @@ static int32_t launch(const AttnArgs& a, cudaStream_t st) {
     const bool use_mma = mma_eligible(a) &&
                          (choice == kMma || (choice == kAuto && (a.S >= 128 || a.B * a.Hq * a.T >= 1024)));
     if (use_mma) {
-        const int32_t rc = launch_mma(a, st);
+        AttnArgs m = a;
+        if (a.n_splits > 1)      // the ticket counters sit behind the partial states (omni_qattn_workspace_bytes)
+            m.work_counter = reinterpret_cast<uint32_t*>(a.ws + (size_t)a.B * a.Hq * a.T * a.n_splits * kWsStride);
+        const int32_t rc = launch_mma(m, st);
         if (rc != OMNI_OK) return rc;
     } else {
         const int64_t n_work = a.B * a.Hq * a.T * a.n_splits;
@@ -308,7 +311,7 @@ using namespace omni;
 
 extern "C" size_t omni_qattn_workspace_bytes(int64_t B, int32_t Hq, int32_t T, int32_t n_splits) {
     if (n_splits <= 1 || B <= 0 || Hq <= 0 || T <= 0) return 0;
-    return (size_t)B * Hq * T * n_splits * kWsStride * sizeof(float);
+    return (size_t)B * Hq * T * n_splits * kWsStride * sizeof(float) + kWorkCounterBytes;
 }
 
 extern "C" int32_t omni_qattn_decode(const void* q, int32_t q_dtype,

@@ -14,9 +14,12 @@ struct AttnArgs {
     float scale; int with_qjl, rotate_q, unrotate_out; int n_splits;
     float* ws; float* out; const uint32_t* g_rows;
     int32_t* status;           // device word set non-zero when a bounded wait expires (may be null)
+    uint32_t* work_counter;    // kWorkCounterBytes of device memory behind the split-K partials: one ticket counter
+                               // per kv head for the tensor-core kernel (null: items are assigned statically)
 };
 
 constexpr int kWsStride = 132;     // floats per split-K partial: 128 accumulators, max, sum, 2 pad
+constexpr size_t kWorkCounterBytes = 4096;   // kSeeds (the most kv heads a call may have) 32-bit counters
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

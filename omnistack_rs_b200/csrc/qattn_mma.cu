@@ -423,8 +423,15 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
     const float qs = a.scale * kLog2e;
     bool alive = true;
 
-    for (int64_t item = (int64_t)blockIdx.x * kMmaWarps + warp; alive && item < n_items;
-         item += (int64_t)gridDim.x * kMmaWarps) {
+    // Work distribution.  Every warp starts on item blockIdx.x * kMmaWarps + warp.  Without a counter the next
+    // item lies one grid of warps further on (equal-sized items: nothing to balance).  With one (split-K calls,
+    // whose items differ in length when the users' caches do) a warp takes a ticket for its next item when it
+    // starts the current one, so the atomic's latency is covered by the item's own work.
+    const int64_t item_stride = (int64_t)gridDim.x * kMmaWarps;
+    uint32_t* const counter = a.work_counter ? a.work_counter + blockIdx.y : nullptr;
+    for (int64_t item = (int64_t)blockIdx.x * kMmaWarps + warp; alive && item < n_items;) {
+        uint32_t ticket = 0u;
+        if (counter && lane == 0) ticket = atomicAdd(counter, 1u);
         int64_t rest = item;
         int hkv = cb_head;
         if (head_in_item) { hkv = (int)(rest % a.Hkv); rest /= a.Hkv; }
@@ -664,6 +671,7 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
                 *reinterpret_cast<float4*>(dst + 4 * mp) = v;
             }
         }
+        item = counter ? item_stride + (int64_t)__shfl_sync(kFullMask, ticket, 0) : item + item_stride;
     }
 
     if (!alive) {
@@ -756,6 +764,7 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     // bound to one head because its lookup table is built from that head's centroids.
     int64_t items, ctas;
     unsigned gy;
+    if (a.work_counter) OMNI_CUDA(cudaMemsetAsync(a.work_counter, 0, kWorkCounterBytes, st));
     if (a.cb_per_head) {
         items = a.B * a.n_splits;
         ctas = sms / a.Hkv > 0 ? sms / a.Hkv : 1;
