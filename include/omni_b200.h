@@ -202,7 +202,7 @@ int32_t omni_qattn_decode_lora(const void* q, int32_t q_dtype,
  * it is not required here) calls cudaMalloc/cudaFree or an allocating library routine.
  *   - the caller still passes every input and the output buffer;
  *   - the scratch array is omni_qattn_noalloc_scratch_bytes() = 32 MiB, enough for
- *     B*Hq*T*n_splits <= 63,550 partial states; larger requests return
+ *     B*Hq*T*n_splits <= 63,542 partial states; larger requests return
  *     OMNI_ERR_UNSUPPORTED with a message (n_splits == 1 needs no scratch and is never
  *     rejected for size); every device that loads the library carries the 33 MiB until exit;
  *   - the FIRST call on each device resolves the arrays' device addresses and uploads the
