@@ -115,6 +115,21 @@ __device__ void build_head_tables(HeadTables& ht, const float* cb_global, int la
 }
 
 // ---- small PTX helpers ------------------------------------------------------------------------
+// Packed fp32 pairs (sm_100): one instruction rounds both halves exactly like the scalar add / fma would, at half
+// the issue slots.  (ax, ay) op (bx, by) -> (dx, dy).
+__device__ __forceinline__ void add2(float& dx, float& dy, float ax, float ay, float bx, float by) {
+    asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n add.rn.f32x2 rd, ra, rb;\n"
+        " mov.b64 {%0, %1}, rd;\n}\n" : "=f"(dx), "=f"(dy) : "f"(ax), "f"(ay), "f"(bx), "f"(by));
+}
+__device__ __forceinline__ void fma2(float& dx, float& dy, float ax, float ay, float bx, float by, float cx, float cy) {
+    asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%6, %7};\n"
+        " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}\n"
+        : "=f"(dx), "=f"(dy) : "f"(ax), "f"(ay), "f"(bx), "f"(by), "f"(cx), "f"(cy));
+}
+__device__ __forceinline__ void mul2(float& dx, float& dy, float ax, float ay, float bx, float by) {
+    asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mul.rn.f32x2 rd, ra, rb;\n"
+        " mov.b64 {%0, %1}, rd;\n}\n" : "=f"(dx), "=f"(dy) : "f"(ax), "f"(ay), "f"(bx), "f"(by));
+}
 __device__ __forceinline__ uint32_t prmt_sign_bytes(uint32_t x) {     // each byte -> 0xFF if its MSB is set, else 0x00
     uint32_t r;
     asm("prmt.b32 %0, %1, %1, 0xBA98;\n" : "=r"(r) : "r"(x));
@@ -143,23 +158,27 @@ __device__ __forceinline__ uint32_t every_fourth_bit(uint32_t w, int s) {
     return x;
 }
 
-// load 32 consecutive elements as fp32
+// 32 consecutive elements of a row, staged as 16-byte chunks and unpacked to fp32
 template <int DT> struct Row32;
 template <> struct Row32<OMNI_F32> {
-    static __device__ __forceinline__ void load(const void* p, int64_t i, float (&y)[32]) {
-        const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    static constexpr int kChunks = 8;
+    static __device__ __forceinline__ const char* addr(const void* p, int64_t i) { return reinterpret_cast<const char*>(reinterpret_cast<const float*>(p) + i); }
+    static __device__ __forceinline__ void unpack(const uint4 (&c)[8], float (&y)[32]) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) { const float4 v = __ldg(q + k); y[4 * k] = v.x; y[4 * k + 1] = v.y; y[4 * k + 2] = v.z; y[4 * k + 3] = v.w; }
+        for (int k = 0; k < 8; ++k) {
+            y[4 * k] = __uint_as_float(c[k].x); y[4 * k + 1] = __uint_as_float(c[k].y);
+            y[4 * k + 2] = __uint_as_float(c[k].z); y[4 * k + 3] = __uint_as_float(c[k].w);
+        }
     }
     static __device__ __forceinline__ void round_pair(float& a, float& b) {}
 };
 template <> struct Row32<OMNI_BF16> {
-    static __device__ __forceinline__ void load(const void* p, int64_t i, float (&y)[32]) {
-        const uint4* q = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+    static constexpr int kChunks = 4;
+    static __device__ __forceinline__ const char* addr(const void* p, int64_t i) { return reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p) + i); }
+    static __device__ __forceinline__ void unpack(const uint4 (&c)[4], float (&y)[32]) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const uint4 v = __ldg(q + k);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            const uint32_t w[4] = {c[k].x, c[k].y, c[k].z, c[k].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 y[8 * k + 2 * j] = __uint_as_float(w[j] << 16);
@@ -174,12 +193,12 @@ template <> struct Row32<OMNI_BF16> {
     }
 };
 template <> struct Row32<OMNI_F16> {
-    static __device__ __forceinline__ void load(const void* p, int64_t i, float (&y)[32]) {
-        const uint4* q = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p) + i);
+    static constexpr int kChunks = 4;
+    static __device__ __forceinline__ const char* addr(const void* p, int64_t i) { return reinterpret_cast<const char*>(reinterpret_cast<const __half*>(p) + i); }
+    static __device__ __forceinline__ void unpack(const uint4 (&c)[4], float (&y)[32]) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const uint4 v = __ldg(q + k);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            const uint32_t w[4] = {c[k].x, c[k].y, c[k].z, c[k].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
@@ -193,6 +212,27 @@ template <> struct Row32<OMNI_F16> {
     }
 };
 
+// Input staging: a lane copies its 32 elements of the NEXT 8-token group into shared memory with cp.async while
+// the current group is being processed, so the global-memory latency is off the critical path.  Layout per warp
+// and buffer: chunk k of lane l at (k * 32 + l) * 16 bytes (conflict-free 16-byte reads).
+constexpr int kStageChunks = 8;                                     // room for the widest element type
+constexpr int kStageBytesPerWarp = kStageChunks * 32 * 16;          // one buffer: it is refilled as soon as it is read
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+template <int DT>
+__device__ __forceinline__ void stage_row(uint32_t buf, const void* x, int64_t i) {
+    const char* src = Row32<DT>::addr(x, i);
+#pragma unroll
+    for (int k = 0; k < Row32<DT>::kChunks; ++k) cp_async16(buf + k * 512, src + 16 * k);
+}
+
 template <int DT, bool ROTATE>
 __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQuantArgs a) {
     extern __shared__ __align__(16) unsigned char fq_smem[];
@@ -202,6 +242,8 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     uint4* gfrag = gfrag_all + (size_t)warp * 16 * 32 + lane;      // this lane's 16 A fragments, 32 uint4 apart
+    const uint32_t stage = (uint32_t)__cvta_generic_to_shared(gfrag_all + (size_t)kFqWarps * 16 * 32) +
+                           warp * kStageBytesPerWarp + lane * 16;  // this lane's chunk 0 of buffer 0
 
     for (int h = warp; h < n_tabs; h += kFqWarps) build_head_tables(tabs[h], a.codebooks + h * 16, lane);
     __syncthreads();
@@ -228,36 +270,55 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
         const int64_t in_base = b * a.xs_b + (int64_t)h * a.xs_h + 32 * t;
         const int64_t out_base = b * a.os_b + (int64_t)h * a.os_h + (a.out_offsets ? a.out_offsets[b] : a.out_offset);
 
+        // rows past the end of a group are clamped to the last token (computed, never stored)
+        if (a.T > 0) stage_row<DT>(stage, a.x, in_base + (g < a.T ? g : a.T - 1) * a.xs_t);
         for (int64_t t0 = 0; t0 < a.T; t0 += 8) {
             const int64_t tr = t0 + g;
             const bool active = tr < a.T;
-            const int64_t trc = active ? tr : a.T - 1;
+            cp_async_wait_all();
             float y[32];
-            Row32<DT>::load(a.x, in_base + trc * a.xs_t, y);
+            {
+                uint4 c[Row32<DT>::kChunks];
+#pragma unroll
+                for (int k = 0; k < Row32<DT>::kChunks; ++k) c[k] = lds_u4(stage + k * 512);
+                if (t0 + 8 < a.T) {                 // the chunks are in registers: refill the buffer with the next group
+                    const int64_t tn = t0 + 8 + g;
+                    stage_row<DT>(stage, a.x, in_base + (tn < a.T ? tn : a.T - 1) * a.xs_t);
+                }
+                Row32<DT>::unpack(c, y);
+            }
             if (ROTATE) {
 #pragma unroll
-                for (int hh = 1; hh < 32; hh <<= 1) {
+                // elements i and i + 16 travel as a packed pair through every stage but h = 16; u - v is
+                // fma(v, -1, u), which rounds exactly like the subtraction
+                for (int hh = 1; hh < 16; hh <<= 1) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < 16; ++i) {
                         if ((i & hh) == 0) {
-                            const float u = y[i], v = y[i | hh];
-                            y[i] = __fadd_rn(u, v);
-                            y[i | hh] = __fsub_rn(u, v);
+                            const float u0 = y[i], u1 = y[i + 16], v0 = y[i | hh], v1 = y[(i | hh) + 16];
+                            add2(y[i], y[i + 16], u0, u1, v0, v1);
+                            fma2(y[i | hh], y[(i | hh) + 16], v0, v1, -1.f, -1.f, u0, u1);
                         }
                     }
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float u = y[i], v = y[i + 16];
+                    y[i] = __fadd_rn(u, v);
+                    y[i + 16] = __fsub_rn(u, v);
                 }
 #pragma unroll
                 for (int m = 1; m <= 2; m <<= 1) {
                     const float sgn = (t & m) ? -1.f : 1.f;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float o = __shfl_xor_sync(kFullMask, y[i], m);
-                        y[i] = __fmaf_rn(sgn, y[i], o);
+                    for (int i = 0; i < 16; ++i) {
+                        const float o0 = __shfl_xor_sync(kFullMask, y[i], m), o1 = __shfl_xor_sync(kFullMask, y[i + 16], m);
+                        fma2(y[i], y[i + 16], sgn, sgn, y[i], y[i + 16], o0, o1);
                     }
                 }
                 const float sc = __uint_as_float(OMNI_WHT_SCALE_BITS);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) y[i] = __fmul_rn(y[i], sc);
+                for (int i = 0; i < 16; ++i) mul2(y[i], y[i + 16], y[i], y[i + 16], sc, sc);
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) Row32<DT>::round_pair(y[i], y[i + 1]);
             }
@@ -285,7 +346,15 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
             // ---- residual norm and fixed-point scale ------------------------------------------------
             float ss = 0.f, emax = 0.f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { ss = fmaf(y[i], y[i], ss); emax = fmaxf(emax, fabsf(y[i])); }
+            {
+                float sa = 0.f, sb = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    fma2(sa, sb, y[i], y[i + 16], y[i], y[i + 16], sa, sb);
+                    emax = fmaxf(emax, fmaxf(fabsf(y[i]), fabsf(y[i + 16])));
+                }
+                ss = sa + sb;
+            }
             ss += __shfl_xor_sync(kFullMask, ss, 1);   ss += __shfl_xor_sync(kFullMask, ss, 2);
             emax = fmaxf(emax, __shfl_xor_sync(kFullMask, emax, 1));
             emax = fmaxf(emax, __shfl_xor_sync(kFullMask, emax, 2));
@@ -297,16 +366,22 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
             // The scale need not be a power of two: the fused multiply-add below rounds e*scale + magic once.
             const float scale = degenerate ? 0.f : __uint_as_float(((uint32_t)(267 - E) << 23) | 0x7F8000u);
             // ---- projections on the int8 tensor cores -------------------------------------------------
+            // The low-limb accumulators start at 64, so that sum64 = 256 * hi + lo is the integer sum plus 64: the
+            // sign test is sum64 >= 64 and the undecided band |sum| <= 64 is one unsigned compare, sum64 <= 128.
             int chi[4][4], clo[4][4];
 #pragma unroll
             for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) { chi[mt][j] = 0; clo[mt][j] = 0; }
+                for (int j = 0; j < 4; ++j) { chi[mt][j] = 0; clo[mt][j] = 64; }
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
+                float v0[8];
+#pragma unroll
+                for (int k = 0; k < 8; k += 2)                                             // low 16 bits = int16
+                    fma2(v0[k], v0[k + 1], y[8 * ks + k], y[8 * ks + k + 1], scale, scale, 12582912.f, 12582912.f);
                 uint32_t v[8];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(fmaf(y[8 * ks + k], scale, 12582912.f));   // low 16 bits = int16
+                for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(v0[k]);
                 const uint32_t p01 = __byte_perm(v[0], v[1], 0x5140), p23 = __byte_perm(v[2], v[3], 0x5140);
                 const uint32_t p45 = __byte_perm(v[4], v[5], 0x5140), p67 = __byte_perm(v[6], v[7], 0x5140);
                 const uint32_t lo0 = __byte_perm(p01, p23, 0x5410), hi0 = __byte_perm(p01, p23, 0x7632);
@@ -319,29 +394,28 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
                 }
             }
             // ---- sign / ambiguity bits: C element (mt, j) = projection 16mt + g + 8(j>>1) of row 2t + (j&1) ----
+            // Ballot words are warp-uniform; lane (row g, quarter t) needs those of m-tile t, column parity g & 1,
+            // halves 0 and 1, and keeps them as the m-tiles go by.
             const bool deg0 = __shfl_sync(kFullMask, (int)degenerate, 8 * t) != 0;         // row 2t   (lanes 8t..)
             const bool deg1 = __shfl_sync(kFullMask, (int)degenerate, 8 * t + 4) != 0;     // row 2t+1
-            uint32_t word_s = 0u, word_a = 0u;                 // lane k < 16 keeps ballot word k = 4mt + j
+            const bool odd = (g & 1) != 0;
+            uint32_t ws0 = 0u, ws1 = 0u, wa0 = 0u, wa1 = 0u;
 #pragma unroll
             for (int mt = 0; mt < 4; ++mt) {
+                uint32_t bs[4], ba[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int sum = chi[mt][j] * 256 + clo[mt][j];
-                    const uint32_t bs = __ballot_sync(kFullMask, sum >= 0);
-                    const uint32_t ba = __ballot_sync(kFullMask, (sum <= 64 && sum >= -64) || ((j & 1) ? deg1 : deg0));
-                    if (lane == mt * 4 + j) { word_s = bs; word_a = ba; }
+                    const int sum64 = chi[mt][j] * 256 + clo[mt][j];
+                    bs[j] = __ballot_sync(kFullMask, sum64 >= 64);
+                    ba[j] = __ballot_sync(kFullMask, (uint32_t)sum64 <= 128u || ((j & 1) ? deg1 : deg0));
                 }
+                const bool mine = (t == mt);
+                ws0 = mine ? (odd ? bs[1] : bs[0]) : ws0; ws1 = mine ? (odd ? bs[3] : bs[2]) : ws1;
+                wa0 = mine ? (odd ? ba[1] : ba[0]) : wa0; wa1 = mine ? (odd ? ba[3] : ba[2]) : wa1;
             }
-            // lane (row g, quarter t) owns projections 16t .. 16t+15: m-tile t, halves j>>1 = 0, 1, column parity g&1
-            uint32_t bits16, amb16;
-            {
-                const int src0 = 4 * t + (g & 1), src1 = src0 + 2;
-                const uint32_t s0 = __shfl_sync(kFullMask, word_s, src0), s1 = __shfl_sync(kFullMask, word_s, src1);
-                const uint32_t a0 = __shfl_sync(kFullMask, word_a, src0), a1 = __shfl_sync(kFullMask, word_a, src1);
-                const int sh = g >> 1;                          // the C owner of this row's columns has t'' = g >> 1
-                bits16 = every_fourth_bit(s0, sh) | (every_fourth_bit(s1, sh) << 8);
-                amb16 = every_fourth_bit(a0, sh) | (every_fourth_bit(a1, sh) << 8);
-            }
+            const int sh = g >> 1;                              // the C owner of this row's columns has t'' = g >> 1
+            uint32_t bits16 = every_fourth_bit(ws0, sh) | (every_fourth_bit(ws1, sh) << 8);
+            uint32_t amb16 = every_fourth_bit(wa0, sh) | (every_fourth_bit(wa1, sh) << 8);
             if (!active) amb16 = 0u;
             // ---- exact recomputation of the undecided projections, one per row at a time ------------------
             uint64_t pending = (uint64_t)__shfl_sync(kFullMask, amb16, 4 * g) |
@@ -393,7 +467,8 @@ static int32_t launch_fast_t(const FastQuantArgs& a, int rotate, cudaStream_t st
     OMNI_CUDA(cudaGetDevice(&dev));
     OMNI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int n_tabs = a.cb_per_head ? a.H : 1;
-    const size_t smem = sizeof(HeadTables) * n_tabs + (size_t)kFqWarps * 16 * 32 * sizeof(uint4);
+    const size_t smem = sizeof(HeadTables) * n_tabs + (size_t)kFqWarps * 16 * 32 * sizeof(uint4) +
+                        (size_t)kFqWarps * kStageBytesPerWarp;
     const int64_t pairs = a.B * a.H;
     int64_t blocks = (pairs + kFqWarps - 1) / kFqWarps;
     if (blocks > 2 * sms) blocks = 2 * sms;
