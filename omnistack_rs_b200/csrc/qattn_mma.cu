@@ -249,7 +249,9 @@ struct WarpState {
 constexpr float kLazyMaxSlack = 6.f;   // log2 units a score may exceed the reference maximum before it is raised
 
 
-template <bool QJL, bool TAIL>
+// ONECOL: the kv head has a single query column (plain decode without query grouping).  Only column 0 of the
+// score tile is real then, so the scalar softmax work of the second column of every lane is left out.
+template <bool QJL, bool TAIL, bool ONECOL>
 __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState& st, const uint32_t (&qB)[8][2],
                                                   const SignB& sg, float post0, float post1,
                                                   uint32_t lut_lane, int nvalid, int kl) {
@@ -281,13 +283,16 @@ __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState&
         imma_s8(d1, neg_bits_s8<0>(sa8), neg_bits_s8<0>(sb8), neg_bits_s8<4>(sa8), neg_bits_s8<4>(sb8),
                 sg.z[2], sg.z[3], d0);
         s00 = post0 * fmaf(kb.na * sg.cs0, (float)d1[0], cd[0] + ce[0]);
-        s01 = post1 * fmaf(kb.na * sg.cs1, (float)d1[1], cd[1] + ce[1]);
         s80 = post0 * fmaf(kb.nb * sg.cs0, (float)d1[2], cd[2] + ce[2]);
-        s81 = post1 * fmaf(kb.nb * sg.cs1, (float)d1[3], cd[3] + ce[3]);
+        if (!ONECOL) {
+            s01 = post1 * fmaf(kb.na * sg.cs1, (float)d1[1], cd[1] + ce[1]);
+            s81 = post1 * fmaf(kb.nb * sg.cs1, (float)d1[3], cd[3] + ce[3]);
+        }
     } else {
-        s00 = post0 * (cd[0] + ce[0]); s01 = post1 * (cd[1] + ce[1]);
-        s80 = post0 * (cd[2] + ce[2]); s81 = post1 * (cd[3] + ce[3]);
+        s00 = post0 * (cd[0] + ce[0]); s80 = post0 * (cd[2] + ce[2]);
+        if (!ONECOL) { s01 = post1 * (cd[1] + ce[1]); s81 = post1 * (cd[3] + ce[3]); }
     }
+    if (ONECOL) { s01 = -INFINITY; s81 = -INFINITY; }
     if (TAIL) {
         if (kl >= nvalid) { s00 = -INFINITY; s01 = -INFINITY; }
         if (kl + 8 >= nvalid) { s80 = -INFINITY; s81 = -INFINITY; }
@@ -295,27 +300,34 @@ __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState&
     // Lazy running maximum: the reference point m of a column is raised only when some score
     // exceeds it by more than kLazyMaxSlack, so the cross-lane reduction and the rescale of the
     // accumulators run on few blocks; in between, weights are at most 2^kLazyMaxSlack.
-    const bool exceed = (fmaxf(s00, s80) > st.m0 + kLazyMaxSlack) || (fmaxf(s01, s81) > st.m1 + kLazyMaxSlack);
+    const bool exceed = (fmaxf(s00, s80) > st.m0 + kLazyMaxSlack) ||
+                        (!ONECOL && fmaxf(s01, s81) > st.m1 + kLazyMaxSlack);
     if (__any_sync(kFullMask, exceed)) {
         float mx0 = fmaxf(s00, s80), mx1 = fmaxf(s01, s81);
 #pragma unroll
         for (int m = 4; m <= 16; m <<= 1) {
             mx0 = fmaxf(mx0, __shfl_xor_sync(kFullMask, mx0, m));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(kFullMask, mx1, m));
+            if (!ONECOL) mx1 = fmaxf(mx1, __shfl_xor_sync(kFullMask, mx1, m));
         }
-        const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
-        const float al0 = ex2_approx(st.m0 - mn0), al1 = ex2_approx(st.m1 - mn1);
-        st.l0 *= al0; st.l1 *= al1;
+        const float mn0 = fmaxf(st.m0, mx0);
+        const float al0 = ex2_approx(st.m0 - mn0);
+        st.l0 *= al0;
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            st.O[mt][0] *= al0; st.O[mt][1] *= al1; st.O[mt][2] *= al0; st.O[mt][3] *= al1;
+        for (int mt = 0; mt < 8; ++mt) { st.O[mt][0] *= al0; st.O[mt][2] *= al0; }
+        st.m0 = mn0;
+        if (!ONECOL) {
+            const float mn1 = fmaxf(st.m1, mx1);
+            const float al1 = ex2_approx(st.m1 - mn1);
+            st.l1 *= al1;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) { st.O[mt][1] *= al1; st.O[mt][3] *= al1; }
+            st.m1 = mn1;
         }
-        st.m0 = mn0; st.m1 = mn1;
     }
-    const float p00 = ex2_approx(s00 - st.m0), p01 = ex2_approx(s01 - st.m1);
-    const float p80 = ex2_approx(s80 - st.m0), p81 = ex2_approx(s81 - st.m1);
+    const float p00 = ex2_approx(s00 - st.m0), p80 = ex2_approx(s80 - st.m0);
+    const float p01 = ONECOL ? 0.f : ex2_approx(s01 - st.m1), p81 = ONECOL ? 0.f : ex2_approx(s81 - st.m1);
     st.l0 += p00 + p80;
-    st.l1 += p01 + p81;
+    if (!ONECOL) st.l1 += p01 + p81;
     // P^T as the B operand: transpose the two 8x8 (key x column) blocks across the warp
     const uint32_t pb0 = movmatrix_trans(pack_half2(p00, p01));
     const uint32_t pb1 = movmatrix_trans(pack_half2(p80, p81));
@@ -370,7 +382,7 @@ __device__ __forceinline__ void ring_consumed(Ring& r) {
     --r.in_flight;
 }
 
-template <int DT, bool QJL>
+template <int DT, bool QJL, bool ONECOL>
 __global__ void __launch_bounds__(kMmaWarps * 32, 1)
 qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v) {
@@ -625,8 +637,8 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
                     load_aux(aux_b, ps + 16 * kQjlBytes, pn + 16);
                 }
             }
-            process_key_block<QJL, false>(kb, st, qB, sg, post0, post1, lut_lane, 16, kr);
-            process_key_block<QJL, false>(kc, st, qB, sg, post0, post1, lut_lane, 16, kr);
+            process_key_block<QJL, false, ONECOL>(kb, st, qB, sg, post0, post1, lut_lane, 16, kr);
+            process_key_block<QJL, false, ONECOL>(kc, st, qB, sg, post0, post1, lut_lane, 16, kr);
             // every lane has consumed its bytes of the stage: it can be refilled
             ring_consumed(ring);
             __syncwarp();
@@ -636,7 +648,7 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         for (int k0 = nstage * kStageKeys; k0 < nkeys; k0 += 16) {     // up to two blocks with plain clamped loads
             const int nvalid = nkeys - k0 < 16 ? nkeys - k0 : 16;
             load_tail_block<QJL>(kb, a, row0 + k0, nvalid, kr, va, vb, g, t);
-            process_key_block<QJL, true>(kb, st, qB, sg, post0, post1, lut_lane, nvalid, kr);
+            process_key_block<QJL, true, ONECOL>(kb, st, qB, sg, post0, post1, lut_lane, nvalid, kr);
         }
 
         // ---- epilogue ----------------------------------------------------------------------
@@ -786,7 +798,9 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
         rc = make_nibble_map(&map_v, a.v_nib);
         if (rc != OMNI_OK) return rc;
     }
-    auto kern = a.with_qjl ? qattn_mma_kernel<DT, true> : qattn_mma_kernel<DT, false>;
+    const bool one_col = (a.Hq / a.Hkv) * a.T == 1;
+    auto kern = a.with_qjl ? (one_col ? qattn_mma_kernel<DT, true, true> : qattn_mma_kernel<DT, true, false>)
+                           : (one_col ? qattn_mma_kernel<DT, false, true> : qattn_mma_kernel<DT, false, false>);
     rc = allow_full_smem(reinterpret_cast<const void*>(kern), dev);
     if (rc != OMNI_OK) return rc;
     kern<<<grid, kMmaWarps * 32, kMmaSmemBytes, st>>>(a, items, map_k, map_v);
