@@ -374,23 +374,28 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
 #pragma unroll
                 for (int j = 0; j < 4; ++j) { chi[mt][j] = 0; clo[mt][j] = 64; }
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                float v0[8];
+            for (int kp = 0; kp < 2; ++kp) {
+                // k-steps kp and kp + 2 together: their elements i and i + 16 are the packed pairs of the rotation
+                float va[8], vb[8];
 #pragma unroll
-                for (int k = 0; k < 8; k += 2)                                             // low 16 bits = int16
-                    fma2(v0[k], v0[k + 1], y[8 * ks + k], y[8 * ks + k + 1], scale, scale, 12582912.f, 12582912.f);
-                uint32_t v[8];
+                for (int k = 0; k < 8; ++k)                                                // low 16 bits = int16
+                    fma2(va[k], vb[k], y[8 * kp + k], y[8 * kp + k + 16], scale, scale, 12582912.f, 12582912.f);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(v0[k]);
-                const uint32_t p01 = __byte_perm(v[0], v[1], 0x5140), p23 = __byte_perm(v[2], v[3], 0x5140);
-                const uint32_t p45 = __byte_perm(v[4], v[5], 0x5140), p67 = __byte_perm(v[6], v[7], 0x5140);
-                const uint32_t lo0 = __byte_perm(p01, p23, 0x5410), hi0 = __byte_perm(p01, p23, 0x7632);
-                const uint32_t lo1 = __byte_perm(p45, p67, 0x5410), hi1 = __byte_perm(p45, p67, 0x7632);
+                for (int half = 0; half < 2; ++half) {
+                    const int ks = kp + 2 * half;
+                    uint32_t v[8];
 #pragma unroll
-                for (int mt = 0; mt < 4; ++mt) {
-                    const uint4 af = gfrag[(mt * 4 + ks) * 32];
-                    imma_s8s8(chi[mt], af, hi0, hi1);
-                    imma_s8u8(clo[mt], af, lo0, lo1);
+                    for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(half ? vb[k] : va[k]);
+                    const uint32_t p01 = __byte_perm(v[0], v[1], 0x5140), p23 = __byte_perm(v[2], v[3], 0x5140);
+                    const uint32_t p45 = __byte_perm(v[4], v[5], 0x5140), p67 = __byte_perm(v[6], v[7], 0x5140);
+                    const uint32_t lo0 = __byte_perm(p01, p23, 0x5410), hi0 = __byte_perm(p01, p23, 0x7632);
+                    const uint32_t lo1 = __byte_perm(p45, p67, 0x5410), hi1 = __byte_perm(p45, p67, 0x7632);
+#pragma unroll
+                    for (int mt = 0; mt < 4; ++mt) {
+                        const uint4 af = gfrag[(mt * 4 + ks) * 32];
+                        imma_s8s8(chi[mt], af, hi0, hi1);
+                        imma_s8u8(clo[mt], af, lo0, lo1);
+                    }
                 }
             }
             // ---- sign / ambiguity bits: C element (mt, j) = projection 16mt + g + 8(j>>1) of row 2t + (j&1) ----
