@@ -431,7 +431,8 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
     const uint32_t off_vb = kStageKeys * kNibBytes + vb * kNibBytes + (((g >> 1) ^ ((vb >> 1) & 3)) << 4) + 8 * (g & 1);
 
     const int Gq = a.Hq / a.Hkv;
-    const int ncols = Gq * a.T;
+    const int ncols_all = Gq * a.T;                 // query columns of a kv head: (q head in group, token)
+    const int n_ctiles = (ncols_all + 7) / 8;       // handled 8 at a time; each tile is a work item of its own
     const float qs = a.scale * kLog2e;
     bool alive = true;
 
@@ -445,6 +446,11 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         uint32_t ticket = 0u;
         if (counter && lane == 0) ticket = atomicAdd(counter, 1u);
         int64_t rest = item;
+        // the column tile varies fastest, so the tiles of one (user, kv head, split) run on neighbouring warps at
+        // about the same time and all but the first find the keys in L2
+        const int col0 = 8 * (int)(rest % n_ctiles);
+        rest /= n_ctiles;
+        const int ncols = ncols_all - col0 < 8 ? ncols_all - col0 : 8;
         int hkv = cb_head;
         if (head_in_item) { hkv = (int)(rest % a.Hkv); rest /= a.Hkv; }
         const int split = (int)(rest % a.n_splits);
@@ -480,7 +486,8 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         // ---- prologue: B operands (scaled queries, q.g projections) --------------------------------
         // 1. every column's query row goes to shared memory in fp32 together with its scalars
         for (int c = 0; c < ncols; ++c) {
-            const int64_t qrow_idx = (b * a.Hq + (int64_t)hkv * Gq + c / a.T) * a.T + (c % a.T);
+            const int cg = col0 + c;
+            const int64_t qrow_idx = (b * a.Hq + (int64_t)hkv * Gq + cg / a.T) * a.T + (cg % a.T);
             float qv[4];
             Elem<DT>::load4(a.q, qrow_idx * kHeadDim + 4 * lane, qv);
             const float amax = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3]))));
@@ -661,7 +668,8 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         for (int j = 0; j < 2; ++j) {
             const int c = 2 * t + j;
             if (c >= ncols) continue;
-            const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + c / a.T) * a.T + (c % a.T);
+            const int cg = col0 + c;
+            const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + cg / a.T) * a.T + (cg % a.T);
             const float l = j ? st.l1 : st.l0;
             const float m = j ? st.m1 : st.m0;
             float* dst;
@@ -734,8 +742,9 @@ static int32_t make_nibble_map(CUtensorMap* map, const uint8_t* base) {
 }
 
 bool mma_eligible(const AttnArgs& a) {
-    const int cols = (a.Hq / a.Hkv) * a.T;
-    return cols <= 8 && !a.rotate_q && !a.unrotate_out && a.Hkv <= 65535;
+    // any number of query columns per kv head: they are processed in tiles of 8 (one MMA N extent)
+    const int64_t cols = (int64_t)(a.Hq / a.Hkv) * a.T;
+    return cols <= 4096 && !a.rotate_q && !a.unrotate_out && a.Hkv <= 65535;
 }
 
 // Per-device facts that never change while the process lives: looked up once, then read without a driver call.
@@ -776,13 +785,14 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     // bound to one head because its lookup table is built from that head's centroids.
     int64_t items, ctas;
     unsigned gy;
+    const int64_t n_ctiles = ((int64_t)(a.Hq / a.Hkv) * a.T + 7) / 8;
     if (a.work_counter) OMNI_CUDA(cudaMemsetAsync(a.work_counter, 0, kWorkCounterBytes, st));
     if (a.cb_per_head) {
-        items = a.B * a.n_splits;
+        items = a.B * a.n_splits * n_ctiles;
         ctas = sms / a.Hkv > 0 ? sms / a.Hkv : 1;
         gy = (unsigned)a.Hkv;
     } else {
-        items = a.B * a.n_splits * a.Hkv;
+        items = a.B * a.n_splits * a.Hkv * n_ctiles;
         ctas = sms;
         gy = 1;
     }

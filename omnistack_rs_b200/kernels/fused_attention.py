@@ -88,10 +88,10 @@ def _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha):
 
 def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int) -> int:
     """Key-axis splits that give every resident warp several work units.  The tensor-core kernel
-    works per (user, kv head) (12 warps on each of 148 SMs); the lane-per-key kernel per
-    (user, query head, token)."""
-    if (Hq // Hkv) * T <= 8 and S >= 128:
-        units, target = B * Hkv, _SM_COUNT * 12 * 8
+    works per (user, kv head, tile of 8 query columns) (12 warps on each of 148 SMs); the lane-per-key
+    kernel per (user, query head, token)."""
+    if S >= 128 or B * Hq * T >= 1024:            # the tensor-core kernel: query columns in tiles of 8
+        units, target = B * Hkv * -(-((Hq // Hkv) * T) // 8), _SM_COUNT * 12 * 8
     else:
         units, target = B * Hq * T, _SM_COUNT * 16 * 2
     if units >= target or S <= 256:

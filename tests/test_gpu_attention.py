@@ -119,7 +119,8 @@ def test_key_count_edges(dev, S):
         assert (out.cpu() - want).abs().max() <= ATOL, (S, ns)
 
 
-@pytest.mark.parametrize("Hq,Hkv,T", [(1, 1, 1), (8, 1, 1), (8, 8, 2), (16, 2, 1), (4, 4, 16)])
+@pytest.mark.parametrize("Hq,Hkv,T", [(1, 1, 1), (8, 1, 1), (8, 8, 2), (16, 2, 1), (4, 4, 16),
+                                      (6, 2, 3), (8, 2, 8), (4, 2, 9), (2, 1, 33)])      # 9, 32, 18 and 66 query columns per kv head
 def test_head_grouping_and_short_prefill(dev, Hq, Hkv, T):
     fa = attn_mod()
     kn, kq, kr, vn, cb, gen = make_cache(3, Hkv, 77, seed=Hq * 10 + T, user_id=2, per_head=(Hkv > 1))
@@ -130,6 +131,8 @@ def test_head_grouping_and_short_prefill(dev, Hq, Hkv, T):
     out16 = fa.omni_attn(*to_dev(dev, q.to(torch.float16), kn, kq, kr, vn, cb), user_id=2, scale=0.11)
     want16 = orc.decode_attention(q.to(torch.float16), kn, kq, kr, vn, cb, 2, 0.11)
     assert (out16.cpu() - want16).abs().max() <= ATOL
+    split = fa.omni_attn(*to_dev(dev, q, kn, kq, kr, vn, cb), user_id=2, scale=0.11, n_splits=3)
+    assert (split.cpu() - want).abs().max() <= ATOL
 
 
 def test_ragged_lengths_slots_and_user_ids(dev):
