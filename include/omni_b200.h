@@ -101,6 +101,15 @@ int32_t omni_dequantize_heads(const uint8_t* nib, const uint8_t* qjl, const floa
                               int64_t is_b, int64_t is_h, int32_t with_qjl,
                               float* out, void* stream);
 
+/* Unpacked QJL residual coding (quantization/qjl.py:78-104 `RademacherQJL.encode`, :106-135 `reconstruct`): one
+ * byte (0/1) per projection, G selected by `seed` = (user_id mod 1024) xor head_idx in [0, 1024).
+ * encode: err device fp32 [n_rows][128] -> signs device u8 [n_rows][64] (1 where the projection is >= 0,
+ * decided in fp64) and norms device fp32 [n_rows].  reconstruct: signs, norms -> out device fp32 [n_rows][128]
+ * = (sum_i (2 signs_i - 1) G[i][d]) * (norm * sqrt(2/pi) / 128).                                              */
+int32_t omni_qjl_encode_bool(const float* err, int64_t n_rows, int32_t seed, uint8_t* signs, float* norms, void* stream);
+int32_t omni_qjl_reconstruct_bool(const uint8_t* signs, const float* norms, int64_t n_rows, int32_t seed, float* out,
+                                  void* stream);
+
 /* Lloyd-Max fit of 16-level codebooks (quantization/codebook.py:64-108 `LloydMaxCalibrator.fit`, :148-172
  * `calibrate_per_group`): equal-mass initialisation, first-index nearest-centroid assignment in fp32, mean
  * update (an empty cell keeps its centroid), stop once the largest move is below `tol` or after `max_iters`

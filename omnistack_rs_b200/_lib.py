@@ -40,6 +40,8 @@ SIGNATURES = {
     "omni_qattn_decode_lora": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
                                       _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
                                       _vp, _sz, _vp, _vp, _vp, _vp]),
+    "omni_qjl_encode_bool": (_i32, [_vp, _i64, _i32, _vp, _vp, _vp]),
+    "omni_qjl_reconstruct_bool": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
     "omni_lloyd_max_workspace_bytes": (_sz, [_i64]),
     "omni_lloyd_max_fit": (_i32, [_vp, _i64, _vp, _i32, _i32, C.c_double, _vp, _sz, _vp, _vp, _vp]),
     "omni_qattn_noalloc_scratch_bytes": (_sz, []),

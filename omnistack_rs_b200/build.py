@@ -14,7 +14,7 @@ import sys
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libomni_b200.so")
-SOURCES = ["runtime.cu", "codec.cu", "codec_fast.cu", "qattn.cu", "qattn_mma.cu", "lora_q.cu", "lloyd_max.cu"]
+SOURCES = ["runtime.cu", "codec.cu", "codec_fast.cu", "qattn.cu", "qattn_mma.cu", "lora_q.cu", "lloyd_max.cu", "qjl_bool.cu"]
 HEADERS = ["common.cuh", "qattn.cuh", "codec_fast.cuh", os.path.join("..", "..", "include", "omni_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -1,4 +1,6 @@
-// Fused decode / short-prefill attention over the packed INT4 + QJL cache.
+// Fused attention over the packed INT4 + QJL cache: the general CUDA-core kernel (small calls and the calls that
+// fold the rotation into q / out), the split-K merge, kernel selection and the C entry points.  The tensor-core
+// kernel that serves every larger call is in qattn_mma.cu.
 //
 // Work unit: one warp per (user, query head, query token, key split).  Lane l walks
 // keys l, l+32, ... of its split with a private online-softmax state (max, sum, 128

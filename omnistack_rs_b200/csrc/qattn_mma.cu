@@ -1,33 +1,34 @@
 // Tensor-core decode attention over the packed INT4 + QJL cache (sm_100a).
 //
-// One warp owns one (user, kv head, key split) and all query columns of that kv head (a
-// column = one (query head of the group, query token); at most 8).  Keys are taken 16 at a
-// time and everything is computed transposed so that the key axis is the MMA "M":
-//     S^T[key, col]  = sum_d  K^[key, d] * q[col, d]                 (8 MMAs, A = dequantised K)
-//                    + norm[key] * sum_i s_i[key] * (q.g_i)[col]      (4 MMAs, A = +-1)
-//     O^T[d,  col]  += sum_key V^[key, d] * P[key, col]               (8 MMAs, A = dequantised V^T)
-// (mma.sync m16n8k16, fp16 operands, fp32 accumulate).
+// One warp owns one (user, kv head, key split, tile of up to 8 query columns); a column is one (query head of
+// the group, query token), and a kv head with more than 8 columns is served by several work items that read the
+// same keys (the later ones from L2).  Keys are taken 16 at a time and everything is computed transposed so that
+// the key axis is the MMA "M":
+//     S^T[key, col]  = sum_d  K^[key, d] * q[col, d]                 (8 fp16 MMAs, A = dequantised K)
+//                    + norm[key] * sum_i s_i[key] * (q.g_i)[col]      (2 int8 MMAs, A = -bit_i, B = q.g in int8)
+//     O^T[d,  col]  += sum_key V^[key, d] * P[key, col]               (8 fp16 MMAs, A = dequantised V^T)
+// (mma.sync m16n8k16 fp16 -> fp32 and m16n8k32 s8 -> s32).
 //
-// Data movement.  The 64-byte nibble rows of K and V are brought in by TMA
-// (cp.async.bulk.tensor.2d, one 16-row box per array and block, 64-byte swizzle) into a
-// private ring of stages per warp, completion tracked by one mbarrier per stage; the lane
-// that issues a copy is lane 0 of the warp that consumes it, so no cross-warp handshake
-// exists.  Sign bytes and norms (12 of the 140 bytes per key) are read with plain loads one
-// block ahead.  Every wait on an mbarrier is bounded; when the bound is hit the warp
-// records it in the status word, waits (bounded again) for its other copies and leaves.
+// Data movement.  The 64-byte nibble rows of K and V are brought in by TMA (cp.async.bulk.tensor.2d, one
+// 32-row box per array and stage = two 16-key blocks, 64-byte swizzle) into a private ring of stages per warp,
+// completion tracked by one mbarrier per stage; the lane that issues a copy is lane 0 of the warp that consumes
+// it, so no cross-warp handshake exists.  Sign bytes and norms (12 of the 140 bytes per key) are read with plain
+// loads one stage ahead, behind one bulk L2 prefetch per work item.  Every wait on an mbarrier is bounded; when
+// the bound is hit the warp records it in the status word, waits (bounded again) for its other copies and leaves.
 //
-// Dequantisation.  A fragments are built straight from the packed bytes with table lookups
-// in shared memory: a 256-entry table maps a byte to half2(cb[low nibble], cb[high nibble]),
-// replicated per lane so every lookup is bank-conflict free; a second table maps a byte made
-// of two 4-bit sign groups to the four half2 of +-1.0 of one MMA.  Both live in one 64 KiB
-// region placed on a 64 KiB boundary of the shared window, so that a single PRMT (byte ->
-// address bits 8..15) forms the complete address.  The contraction index of each MMA is a
-// permutation of d (or of the projections) chosen so that each thread reads 16 contiguous
-// bytes of a key row; for V the two nibbles of a pair come from two different keys and the
-// index byte is formed with one shift and one LOP3 per four lookups.  The rows of the score
-// tile are a permutation rho of the 16 keys chosen so that (a) the transposed softmax
-// weights come out of MOVMATRIX in the order the V fragments need and (b) every shared-memory
+// Dequantisation.  A fragments are built straight from the packed bytes with table lookups in shared memory: a
+// 256-entry table maps a byte to half2(cb[low nibble], cb[high nibble]), replicated per lane so every lookup is
+// bank-conflict free.  The table takes a 64 KiB region placed on a 64 KiB boundary of the shared window, so that
+// a single PRMT (byte -> address bits 8..15) forms the complete address.  The contraction index of each MMA is a
+// permutation of d chosen so that each thread reads 16 contiguous bytes of a key row; for V the two nibbles of a
+// pair come from two different keys and the index byte is formed with one shift and one LOP3 per four lookups.
+// The 64 sign bits of a key become int8 operands in registers (a multiply spreads 4 bits to the byte MSBs, PRMT
+// replicates them).  The rows of the score tile are a permutation rho of the 16 keys chosen so that (a) the
+// transposed softmax weights come out of MOVMATRIX in the order the V fragments need and (b) every shared-memory
 // read of a stage is conflict free under the 64-byte swizzle.
+//
+// Work distribution.  Persistent grid, one CTA per SM.  Calls without key splits assign items statically (equal
+// sizes); split-K calls draw tickets from a counter in the workspace so ragged cache lengths stay balanced.
 #include "qattn.cuh"
 #include <cuda.h>
 #include <mutex>

@@ -3,9 +3,9 @@
 Mirrors ``omnistack_rs/quantization/qjl.py`` of the reference (``RademacherQJL`` :46,
 ``qjl_encode`` :136, ``qjl_reconstruct`` :162).  G comes from the library's MT19937 table
 (seed ``(user_id % 1024) ^ head_idx``), so it is the matrix the reference draws with a CPU
-``torch.Generator`` whatever device the data is on.  The projections run as one dense
-product on the device; the packed, fused form of the same arithmetic is
-``kernels.quantize.quantize_heads``.
+``torch.Generator`` whatever device the data is on.  ``encode`` and ``reconstruct`` run the
+``omni_qjl_encode_bool`` / ``omni_qjl_reconstruct_bool`` kernels; the packed, fused form of the
+same arithmetic is ``kernels.quantize.quantize_heads``.
 """
 from __future__ import annotations
 
@@ -41,19 +41,42 @@ class RademacherQJL:
         seed = (user_id % 1024) ^ head_idx
         return (_g_bits(seed).to(device=device, dtype=dtype) * 2 - 1)
 
+    @staticmethod
+    def _seed(head_idx: int, user_id: int) -> int:
+        seed = (int(user_id) % 1024) ^ int(head_idx)
+        if not 0 <= seed < 1024:
+            raise NotImplementedError(f"seed {seed} outside the 1024-seed table (head_idx must be < 1024)")
+        return seed
+
     def encode(self, error: torch.Tensor, head_idx: int, user_id: int = 0):
-        _lib.require_cuda(error)
-        err = error.float()
-        G = self._make_G(head_idx, error.device, torch.float64, user_id)
-        signs = (err.double() @ G.t()) >= 0
-        norms = err.norm(dim=-1, keepdim=True).to(error.dtype)
-        return signs, norms
+        dev = _lib.require_cuda(error)
+        lib = _lib.ensure_init(dev)
+        if error.shape[-1] != self.head_dim:
+            raise ValueError(f"last dim must be head_dim={self.head_dim}, got {error.shape[-1]}")
+        err = error.float().contiguous()
+        n = err.numel() // self.head_dim
+        signs = torch.empty(*error.shape[:-1], self.qjl_dim, dtype=torch.uint8, device=dev)
+        norms = torch.empty(*error.shape[:-1], 1, dtype=torch.float32, device=dev)
+        with _lib.on_device(dev):
+            _lib.check(lib.omni_qjl_encode_bool(_lib.ptr(err), n, self._seed(head_idx, user_id), _lib.ptr(signs),
+                                                _lib.ptr(norms), _lib.stream_ptr(dev)))
+        return signs.view(torch.bool), norms.to(error.dtype)
 
     def reconstruct(self, signs: torch.Tensor, norms: torch.Tensor, head_idx: int, user_id: int = 0):
-        _lib.require_cuda(signs)
-        G = self._make_G(head_idx, signs.device, torch.float32, user_id)
-        b = signs.float() * 2.0 - 1.0
-        return (b @ G) * (norms.float() * math.sqrt(2.0 / math.pi) / self.head_dim)
+        dev = _lib.require_cuda(signs, norms)
+        lib = _lib.ensure_init(dev)
+        if signs.shape[-1] != self.qjl_dim:
+            raise ValueError(f"last dim of signs must be qjl_dim={self.qjl_dim}, got {signs.shape[-1]}")
+        sg = signs.to(torch.uint8).contiguous()
+        nr = norms.float().contiguous()
+        n = sg.numel() // self.qjl_dim
+        if nr.numel() != n:
+            raise ValueError("norms must hold one value per sign row")
+        out = torch.empty(*signs.shape[:-1], self.head_dim, dtype=torch.float32, device=dev)
+        with _lib.on_device(dev):
+            _lib.check(lib.omni_qjl_reconstruct_bool(_lib.ptr(sg), _lib.ptr(nr), n, self._seed(head_idx, user_id),
+                                                     _lib.ptr(out), _lib.stream_ptr(dev)))
+        return out
 
 
 def qjl_encode(x_orig, x_dequant, head_idx: int, qjl_dim: int = 64, user_id: int = 0):
