@@ -345,7 +345,6 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
             }
             // ---- residual norm and fixed-point scale ------------------------------------------------
             float ss = 0.f, emax = 0.f;
-#pragma unroll
             {
                 float sa = 0.f, sb = 0.f;
 #pragma unroll
