@@ -467,7 +467,9 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         const int64_t slot = a.cache_slots ? (int64_t)a.cache_slots[b] : b;
         const int64_t row0 = slot * a.ks_b + (int64_t)hkv * a.ks_h + s0;
         const int nkeys = s1 > s0 ? (int)(s1 - s0) : 0;
-        const int nstage = nkeys / kStageKeys;                 // full stages; the rest (< 32 keys) uses plain loads
+        // full stages come in by TMA, whose row coordinate is a signed 32-bit number; the rest (fewer than 32 keys,
+        // or every key of a range that lies beyond that coordinate space) is read with plain loads
+        const int nstage = (row0 + nkeys <= 0x7fffffffLL) ? nkeys / kStageKeys : 0;
         {
             const int prime = nstage < kStages ? nstage : kStages;
             for (int j = 0; j < prime; ++j) ring_issue(ring, &map_k, &map_v, (int32_t)(row0 + kStageKeys * j), lane);
@@ -653,7 +655,7 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
             if (j + kStages < nstage) ring_issue(ring, &map_k, &map_v, (int32_t)(row0 + kStageKeys * (j + kStages)), lane);
         }
         if (!alive) break;
-        for (int k0 = nstage * kStageKeys; k0 < nkeys; k0 += 16) {     // up to two blocks with plain clamped loads
+        for (int k0 = nstage * kStageKeys; k0 < nkeys; k0 += 16) {     // blocks with plain clamped loads
             const int nvalid = nkeys - k0 < 16 ? nkeys - k0 : 16;
             load_tail_block<QJL>(kb, a, row0 + k0, nvalid, kr, va, vb, g, t);
             process_key_block<QJL, true, ONECOL>(kb, st, qB, sg, post0, post1, lut_lane, nvalid, kr);
