@@ -30,7 +30,8 @@ struct HeadTables {
     uint8_t cell[32];       // code at the low end of each grid cell
     float inv32, off32;     // cell(y) = rn(31 * sat(y * inv32 + off32))
     float guard;            // |y| <= guard: the threshold shortcut is valid
-    int valid;              // 0: this codebook always takes the defining scan
+    int valid;              // 0: this codebook always takes the defining scan; 1: grid cell + one compare;
+                            // 2: binary search over the 15 exact thresholds (the grid cannot resolve them)
     int pad[4];
 };
 static_assert(sizeof(HeadTables) % 16 == 0, "HeadTables must keep 16-byte alignment in an array");
@@ -70,7 +71,7 @@ __device__ void build_head_tables(HeadTables& ht, const float* cb_global, int la
     for (int m = 16; m >= 1; m >>= 1) gap = fminf(gap, __shfl_xor_sync(kFullMask, gap, m));
     const float maxabs = fmaxf(fabsf(ht.cb[0]), fabsf(ht.cb[15]));
     const float guard = gap * 1048576.f;
-    bool ok = __all_sync(kFullMask, ordered && finite) && gap > 0.f && isfinite(guard) && guard >= 4.f * maxabs;
+    bool ok = __all_sync(kFullMask, ordered && finite) && gap > 0.f;
     if (!ok) {                                       // uniform: every element of this head is scanned
         if (lane == 0) { ht.valid = 0; ht.guard = -1.f; ht.inv32 = 0.f; ht.off32 = 0.f; }
         __syncwarp();
@@ -88,6 +89,11 @@ __device__ void build_head_tables(HeadTables& ht, const float* cb_global, int la
     if (lane == 16) ht.thr[16] = INFINITY;
     if (lane == 0) ht.thr[0] = -INFINITY;
     __syncwarp();
+    if (!(isfinite(guard) && guard >= 4.f * maxabs)) {   // uniform: gaps too small for the grid, thresholds still exact
+        if (lane == 0) { ht.valid = 2; ht.guard = 3.0e38f; ht.inv32 = 0.f; ht.off32 = 0.f; }
+        __syncwarp();
+        return;
+    }
     const float t1 = ht.thr[1], t15 = ht.thr[15];
     const float margin = (t15 - t1) * (1.f / 29.f);
     const float lo_y = t1 - margin, hi_y = t15 + margin;
@@ -110,7 +116,9 @@ __device__ void build_head_tables(HeadTables& ht, const float* cb_global, int la
     ok = __all_sync(kFullMask, top - base <= 1 && top >= base) &&
          cell_of(-guard, inv32, off32) == 0 && cell_of(guard, inv32, off32) == 31;
     ht.cell[lane] = (uint8_t)base;
-    if (lane == 0) { ht.valid = ok ? 1 : 0; ht.guard = ok ? guard : -1.f; ht.inv32 = inv32; ht.off32 = off32; }
+    // A grid that cannot separate the thresholds (two of them in one cell) leaves the exact thresholds usable
+    // by themselves: such codebooks take the four-step binary search, for every finite y.
+    if (lane == 0) { ht.valid = ok ? 1 : 2; ht.guard = ok ? guard : 3.0e38f; ht.inv32 = inv32; ht.off32 = off32; }
     __syncwarp();
 }
 
@@ -331,6 +339,16 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int c = code_by_scan(y[i], ht.cb);
+                    codes[i >> 3] |= (uint32_t)c << (4 * (i & 7));
+                    y[i] = __fsub_rn(y[i], ht.cb[c]);
+                }
+            } else if (ht.valid == 2) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {                 // code = number of thresholds thr[1..15] that are <= y
+                    int c = (y[i] >= ht.thr[8]) ? 8 : 0;
+                    c += (y[i] >= ht.thr[c + 4]) ? 4 : 0;
+                    c += (y[i] >= ht.thr[c + 2]) ? 2 : 0;
+                    c += (y[i] >= ht.thr[c + 1]) ? 1 : 0;
                     codes[i >> 3] |= (uint32_t)c << (4 * (i & 7));
                     y[i] = __fsub_rn(y[i], ht.cb[c]);
                 }

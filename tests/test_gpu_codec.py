@@ -160,6 +160,30 @@ def test_edge_values(dev):
         check_packed(quant.quantize_heads(y.to(dev), cb2.to(dev), 3), want[:3], want[3], 3)
 
 
+@pytest.mark.parametrize("kind", ["tight_pair", "clustered", "tiny_gaps", "wide_tail"])
+def test_codebooks_the_grid_cannot_resolve(dev, kind):
+    """Codebooks whose thresholds crowd into one cell of the fast kernel's grid (or whose gaps are far below the
+    range) must still give the reference's codes: the kernel falls back to the exact thresholds or the scan."""
+    quant, _ = k()
+    gen = torch.Generator().manual_seed(21)
+    if kind == "tight_pair":
+        cb = torch.linspace(-2.5, 2.5, 16)
+        cb[8] = cb[7] + 1e-4
+    elif kind == "clustered":
+        cb = torch.cat([torch.linspace(-3, -2.9, 6), torch.linspace(-0.05, 0.05, 5), torch.linspace(2.0, 4.0, 5)])
+    elif kind == "tiny_gaps":
+        cb = torch.arange(16, dtype=torch.float32) * 3e-7 + 1.0
+    else:
+        cb = torch.cat([torch.linspace(-1, 1, 15), torch.tensor([1e6])])
+    y = orc.wht128(torch.randn(2, 1, 40, 128, generator=gen))
+    y[0, 0, 0, :16] = cb                                        # exact centroids
+    y[0, 0, 1, :15] = (cb[1:] + cb[:-1]) / 2                    # fp32 midpoints
+    y[1, 0, 2, :16] = torch.nextafter(cb, torch.full_like(cb, 1e9))
+    want = orc.quantize_heads(y, cb, 9, return_residual=True)
+    got = quant.quantize_heads(y.to(dev), cb.to(dev), 9)
+    check_packed(got, want[:3], want[3], 9)
+
+
 def test_empty_and_strided_inputs(dev):
     quant, _ = k()
     cb = torch.linspace(-3, 3, 16).to(dev)
