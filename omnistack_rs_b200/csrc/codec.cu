@@ -166,6 +166,64 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) dequantize_kernel(CodecAr
     }
 }
 
+// Head-seeded dequantisation, the streaming form: a warp takes a run of consecutive tokens of one (user, head), so
+// the head's 16 centroids (one per lane, fetched by shuffle) and this lane's four columns of G stay in registers
+// for the whole run; per token it reads 2 bytes of codes per lane plus the broadcast sign word and norm, and
+// writes 16 bytes per lane.  Two tokens are in flight per iteration.
+constexpr int kDeqRun = 64;     // tokens per work unit
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) dequantize_heads_kernel(CodecArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t runs_per_head = (a.T + kDeqRun - 1) / kDeqRun;
+    const int64_t n_units = a.B * a.H * runs_per_head;
+    const int64_t nw = (int64_t)gridDim.x * kWarpsPerBlock;
+    for (int64_t u = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); u < n_units; u += nw) {
+        const int64_t run = u % runs_per_head, bh = u / runs_per_head;
+        const int h = (int)(bh % a.H);
+        const int64_t b = bh / a.H;
+        const float cb_lane = __ldg(a.codebooks + (a.cb_per_head ? h * 16 : 0) + (lane & 15));
+        uint64_t gc[4] = {0ull, 0ull, 0ull, 0ull};
+        if (a.with_qjl) {
+            const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
+            const uint64_t* gp = a.g_cols + (size_t)seed_of(uid, h) * kHeadDim + 4 * lane;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) gc[k] = __ldg(gp + k);
+        }
+        const int64_t t_begin = run * kDeqRun, t_end = (t_begin + kDeqRun < a.T) ? t_begin + kDeqRun : a.T;
+        const int64_t in0 = b * a.os_b + h * a.os_h, out0 = (b * a.H + h) * a.T;
+        for (int64_t t = t_begin; t < t_end; t += 2) {
+            const bool two = t + 1 < t_end;
+            const int64_t r0 = in0 + t, r1 = in0 + (two ? t + 1 : t);
+            const uint32_t p0 = reinterpret_cast<const uint16_t*>(a.nib + r0 * kNibBytes)[lane];
+            const uint32_t p1 = reinterpret_cast<const uint16_t*>(a.nib + r1 * kNibBytes)[lane];
+            uint2 s0 = make_uint2(0u, 0u), s1 = make_uint2(0u, 0u);
+            float c0 = 0.f, c1 = 0.f;
+            if (a.with_qjl) {
+                s0 = *reinterpret_cast<const uint2*>(a.qjl + r0 * kQjlBytes);
+                s1 = *reinterpret_cast<const uint2*>(a.qjl + r1 * kQjlBytes);
+                c0 = __fmul_rn(a.norms[r0], kQjlCoef);
+                c1 = __fmul_rn(a.norms[r1], kQjlCoef);
+            }
+            float v0[4], v1[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                v0[k] = __shfl_sync(kFullMask, cb_lane, (p0 >> (4 * k)) & 0xF);
+                v1[k] = __shfl_sync(kFullMask, cb_lane, (p1 >> (4 * k)) & 0xF);
+            }
+            if (a.with_qjl) {
+                const uint64_t sig0 = ((uint64_t)s0.y << 32) | s0.x, sig1 = ((uint64_t)s1.y << 32) | s1.x;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {       // sum_i s_i * g_id with s, g in {-1,+1}: matches minus mismatches
+                    v0[k] = __fadd_rn(v0[k], __fmul_rn((float)(kQjlDim - 2 * __popcll(sig0 ^ gc[k])), c0));
+                    v1[k] = __fadd_rn(v1[k], __fmul_rn((float)(kQjlDim - 2 * __popcll(sig1 ^ gc[k])), c1));
+                }
+            }
+            *reinterpret_cast<float4*>(a.out + (out0 + t) * kHeadDim + 4 * lane) = make_float4(v0[0], v0[1], v0[2], v0[3]);
+            if (two) *reinterpret_cast<float4*>(a.out + (out0 + t + 1) * kHeadDim + 4 * lane) = make_float4(v1[0], v1[1], v1[2], v1[3]);
+        }
+    }
+}
+
 static int grid_for_rows(int64_t n_rows) {
     int64_t blocks = (n_rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
     const int64_t cap = 148 * 8 * 4;     // a few resident waves of 256-thread blocks per SM
@@ -278,6 +336,11 @@ static int32_t dequantize_common(CodecArgs& a, void* stream) {
     const DeviceTables* tb = tables_for_current_device();
     if (!tb) return OMNI_ERR_NOT_INIT;
     a.g_rows = tb->rows; a.g_cols = tb->cols;
+    if (!a.row_seeded) {
+        const int grid = grid_for_rows(a.B * a.H * ((a.T + kDeqRun - 1) / kDeqRun));
+        dequantize_heads_kernel<<<grid, kWarpsPerBlock * 32, 0, (cudaStream_t)stream>>>(a);
+        return check_cuda(cudaGetLastError(), "dequantize_heads_kernel launch");
+    }
     const int grid = grid_for_rows(a.B * a.H * a.T);
     dequantize_kernel<<<grid, kWarpsPerBlock * 32, 0, (cudaStream_t)stream>>>(a);
     return check_cuda(cudaGetLastError(), "dequantize_kernel launch");
