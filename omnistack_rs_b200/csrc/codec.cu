@@ -277,6 +277,12 @@ extern "C" int32_t omni_rotate(const void* x, void* y, int64_t n_rows, int32_t d
     OMNI_REQUIRE(x && y, OMNI_ERR_ARG, "omni_rotate: NULL buffer");
     OMNI_REQUIRE(aligned(x, 16) && aligned(y, 16), OMNI_ERR_ARG, "omni_rotate: buffers must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
+    // 16-bit rows: 8 rows per warp (fewer cross-lane stages; the warp-per-row kernel is shuffle-bound there).
+    // fp32 rows: warp per row, whose 16-byte accesses are fully coalesced (98 % of the copy peak).
+    // OMNI_ROTATE_KERNEL=rows8|warp forces one of them (tests).
+    const char* forced = getenv("OMNI_ROTATE_KERNEL");
+    const bool rows8 = forced ? forced[0] == 'r' : dtype != OMNI_F32;
+    if (rows8) return launch_fast_rotate(x, y, n_rows, dtype, st);
     const int grid = grid_for_rows(n_rows);
     switch (dtype) {
         case OMNI_F32:  rotate_kernel<OMNI_F32><<<grid, kWarpsPerBlock * 32, 0, st>>>(x, y, n_rows); break;

@@ -179,6 +179,11 @@ template <> struct Row32<OMNI_F32> {
         }
     }
     static __device__ __forceinline__ void round_pair(float& a, float& b) {}
+    static __device__ __forceinline__ void pack(const float (&y)[32], uint4 (&c)[8]) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            c[k] = make_uint4(__float_as_uint(y[4 * k]), __float_as_uint(y[4 * k + 1]), __float_as_uint(y[4 * k + 2]), __float_as_uint(y[4 * k + 3]));
+    }
 };
 template <> struct Row32<OMNI_BF16> {
     static constexpr int kChunks = 4;
@@ -199,6 +204,18 @@ template <> struct Row32<OMNI_BF16> {
         const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
         a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u);
     }
+    static __device__ __forceinline__ void pack(const float (&y)[32], uint4 (&c)[4]) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(y[8 * k + 2 * j], y[8 * k + 2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            c[k] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
 };
 template <> struct Row32<OMNI_F16> {
     static constexpr int kChunks = 4;
@@ -218,7 +235,57 @@ template <> struct Row32<OMNI_F16> {
         const float2 f = __half22float2(__floats2half2_rn(a, b));
         a = f.x; b = f.y;
     }
+    static __device__ __forceinline__ void pack(const float (&y)[32], uint4 (&c)[4]) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 h = __floats2half2_rn(y[8 * k + 2 * j], y[8 * k + 2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            c[k] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
 };
+
+// Normalised 128-point Walsh-Hadamard transform of a row held by four lanes (lane t = elements 32t .. 32t+31),
+// in the reference's stage order with one rounding per add / subtract; the result is not yet rounded to the
+// element type.
+__device__ __forceinline__ void rotate_row32(float (&y)[32], int t) {
+    // elements i and i + 16 travel as a packed pair through every stage but h = 16; u - v is fma(v, -1, u),
+    // which rounds exactly like the subtraction
+#pragma unroll
+    for (int hh = 1; hh < 16; hh <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if ((i & hh) == 0) {
+                const float u0 = y[i], u1 = y[i + 16], v0 = y[i | hh], v1 = y[(i | hh) + 16];
+                add2(y[i], y[i + 16], u0, u1, v0, v1);
+                fma2(y[i | hh], y[(i | hh) + 16], v0, v1, -1.f, -1.f, u0, u1);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float u = y[i], v = y[i + 16];
+        y[i] = __fadd_rn(u, v);
+        y[i + 16] = __fsub_rn(u, v);
+    }
+    // the two stages across the row's four lanes: fma(+-1, mine, partner) rounds like the add / subtract
+#pragma unroll
+    for (int m = 1; m <= 2; m <<= 1) {
+        const float sgn = (t & m) ? -1.f : 1.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float o0 = __shfl_xor_sync(kFullMask, y[i], m), o1 = __shfl_xor_sync(kFullMask, y[i + 16], m);
+            fma2(y[i], y[i + 16], sgn, sgn, y[i], y[i + 16], o0, o1);
+        }
+    }
+    const float sc = __uint_as_float(OMNI_WHT_SCALE_BITS);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) mul2(y[i], y[i + 16], y[i], y[i + 16], sc, sc);
+}
 
 // Input staging: a lane copies its 32 elements of the NEXT 8-token group into shared memory with cp.async while
 // the current group is being processed, so the global-memory latency is off the critical path.  Layout per warp
@@ -296,37 +363,7 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
                 Row32<DT>::unpack(c, y);
             }
             if (ROTATE) {
-#pragma unroll
-                // elements i and i + 16 travel as a packed pair through every stage but h = 16; u - v is
-                // fma(v, -1, u), which rounds exactly like the subtraction
-                for (int hh = 1; hh < 16; hh <<= 1) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        if ((i & hh) == 0) {
-                            const float u0 = y[i], u1 = y[i + 16], v0 = y[i | hh], v1 = y[(i | hh) + 16];
-                            add2(y[i], y[i + 16], u0, u1, v0, v1);
-                            fma2(y[i | hh], y[(i | hh) + 16], v0, v1, -1.f, -1.f, u0, u1);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float u = y[i], v = y[i + 16];
-                    y[i] = __fadd_rn(u, v);
-                    y[i + 16] = __fsub_rn(u, v);
-                }
-#pragma unroll
-                for (int m = 1; m <= 2; m <<= 1) {
-                    const float sgn = (t & m) ? -1.f : 1.f;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float o0 = __shfl_xor_sync(kFullMask, y[i], m), o1 = __shfl_xor_sync(kFullMask, y[i + 16], m);
-                        fma2(y[i], y[i + 16], sgn, sgn, y[i], y[i + 16], o0, o1);
-                    }
-                }
-                const float sc = __uint_as_float(OMNI_WHT_SCALE_BITS);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) mul2(y[i], y[i + 16], y[i], y[i + 16], sc, sc);
+                rotate_row32(y, t);
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) Row32<DT>::round_pair(y[i], y[i + 1]);
             }
@@ -468,6 +505,47 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
             }
         }
     }
+}
+
+// Stand-alone rotation with the same row layout (8 rows per warp, 4 lanes per row, 16-byte loads and stores): two
+// cross-lane stages instead of five, which matters for 16-bit rows, where the warp-per-row kernel is bound by
+// shuffle throughput.
+template <int DT>
+__global__ void __launch_bounds__(kFqWarps * 32) fast_rotate_kernel(const void* x, void* y_out, int64_t n_rows) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t n_groups = (n_rows + 7) / 8;
+    for (int64_t grp = (int64_t)blockIdx.x * kFqWarps + warp; grp < n_groups; grp += (int64_t)gridDim.x * kFqWarps) {
+        const int64_t row = grp * 8 + g;
+        const bool active = row < n_rows;
+        const int64_t rc = active ? row : n_rows - 1;
+        uint4 c[Row32<DT>::kChunks];
+        const uint4* src = reinterpret_cast<const uint4*>(Row32<DT>::addr(x, rc * kHeadDim + 32 * t));
+#pragma unroll
+        for (int k = 0; k < Row32<DT>::kChunks; ++k) c[k] = __ldg(src + k);
+        float y[32];
+        Row32<DT>::unpack(c, y);
+        rotate_row32(y, t);
+        Row32<DT>::pack(y, c);
+        if (active) {
+            uint4* dst = reinterpret_cast<uint4*>(const_cast<char*>(Row32<DT>::addr(y_out, rc * kHeadDim + 32 * t)));
+#pragma unroll
+            for (int k = 0; k < Row32<DT>::kChunks; ++k) dst[k] = c[k];
+        }
+    }
+}
+
+int32_t launch_fast_rotate(const void* x, void* y, int64_t n_rows, int dtype, cudaStream_t st) {
+    int64_t blocks = ((n_rows + 7) / 8 + kFqWarps - 1) / kFqWarps;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+    switch (dtype) {
+        case OMNI_F32:  fast_rotate_kernel<OMNI_F32><<<(unsigned)blocks, kFqWarps * 32, 0, st>>>(x, y, n_rows); break;
+        case OMNI_BF16: fast_rotate_kernel<OMNI_BF16><<<(unsigned)blocks, kFqWarps * 32, 0, st>>>(x, y, n_rows); break;
+        case OMNI_F16:  fast_rotate_kernel<OMNI_F16><<<(unsigned)blocks, kFqWarps * 32, 0, st>>>(x, y, n_rows); break;
+        default: return set_error(OMNI_ERR_ARG, "omni_rotate: unknown dtype code %d", dtype);
+    }
+    return check_cuda(cudaGetLastError(), "fast_rotate_kernel launch");
 }
 
 // ---- host side ------------------------------------------------------------------------------------

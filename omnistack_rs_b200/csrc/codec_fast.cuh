@@ -18,4 +18,7 @@ struct FastQuantArgs {
 bool fast_quantize_eligible(const FastQuantArgs& a, int dtype);
 int32_t launch_fast_quantize(const FastQuantArgs& a, int dtype, int rotate, cudaStream_t st);
 
+// stand-alone rotation of n_rows contiguous rows (16-byte aligned buffers)
+int32_t launch_fast_rotate(const void* x, void* y, int64_t n_rows, int dtype, cudaStream_t st);
+
 }  // namespace omni

@@ -45,7 +45,10 @@ def check_packed(got, want, resid=None, user_id=0):
     assert torch.allclose(gr, wr, rtol=NORM_RTOL, atol=1e-30)
 
 
-def test_rotation_bit_exact(dev):
+@pytest.mark.parametrize("rotate_kernel", ["rows8", "warp"])
+def test_rotation_bit_exact(dev, rotate_kernel, monkeypatch):
+    """Both stand-alone rotation kernels (8 rows per warp, the default; one row per warp) against the fixtures."""
+    monkeypatch.setenv("OMNI_ROTATE_KERNEL", rotate_kernel)
     _, had = k()
     g = load_golden("rotation.npz")
     x = t(g["x"])
@@ -55,6 +58,11 @@ def test_rotation_bit_exact(dev):
     xk = torch.randn(2, 3, 5, 128)
     a, b = had.rotate_kv_cache(xk.to(dev), (2 * xk).to(dev))
     assert torch.equal(a.cpu(), orc.wht128(xk)) and torch.equal(b.cpu(), orc.wht128(2 * xk))
+    for n in (1, 7, 8, 9, 1000):                                   # row counts around the 8-row groups, all dtypes
+        for dt in (torch.float32, torch.bfloat16, torch.float16):
+            xr = (torch.randn(n, 128, generator=torch.Generator().manual_seed(n)) * 3).to(dt)
+            got = had.rotate_queries(xr.to(dev)).cpu()
+            assert got.dtype == dt and torch.equal(got, orc.wht128(xr)), (n, dt)
     with pytest.raises(ValueError, match="head_dim"):
         had.rotate_queries(torch.zeros(2, 64, device=dev))
 
