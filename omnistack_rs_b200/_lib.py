@@ -148,6 +148,20 @@ def stream_ptr(device: torch.device):
     return torch._C._cuda_getCurrentRawStream(idx) or None
 
 
+_workspaces = {}
+
+
+def workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    """Grow-only scratch of at least ``nbytes`` bytes, one per (device, stream): calls on one stream run in order,
+    so they can share it; calls on different streams get different buffers."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream or 0)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() * 4 < nbytes:
+        buf = torch.empty(max((nbytes + 3) // 4, 1 << 16), dtype=torch.float32, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
 def as_device(x: torch.Tensor, device: torch.device, dtype: torch.dtype) -> torch.Tensor:
     """``x`` as a contiguous tensor of ``dtype`` on ``device``; ``x`` itself when it already is one."""
     if x.dtype is dtype and x.device == device and x.is_contiguous():

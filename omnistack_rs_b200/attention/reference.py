@@ -3,7 +3,8 @@
 Mirrors ``reference_attn`` (:72) and ``repeat_kv`` (:49) of the reference's
 ``omnistack_rs/attention/reference.py``: tile-wise running (max, sum, accumulator) update
 in float32, additive ``mask``, result cast to ``q.dtype``.  It operates on dense K/V and
-is independent of the quantized path; it runs on the device its inputs live on.
+is independent of the quantized path: a check for the packed kernels, run with torch operations
+on the CUDA device its inputs live on (host tensors raise, like everywhere in this package).
 """
 from __future__ import annotations
 
@@ -11,6 +12,8 @@ import math
 from typing import Optional
 
 import torch
+
+from .. import _lib
 
 
 def repeat_kv(x: torch.Tensor, n_groups: int) -> torch.Tensor:
@@ -22,6 +25,7 @@ def repeat_kv(x: torch.Tensor, n_groups: int) -> torch.Tensor:
 
 def reference_attn(q, k, v, mask: Optional[torch.Tensor] = None, scale: Optional[float] = None,
                    tile_size: int = 128) -> torch.Tensor:
+    _lib.require_cuda(q, k, v, mask)
     n_groups = q.shape[1] // k.shape[1]
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])

@@ -131,8 +131,9 @@ def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, w
         ws_bytes = lib.omni_qattn_lora_workspace_bytes(B, Hq, T, n_splits)
     elif n_splits > 1:
         ws_bytes = lib.omni_qattn_workspace_bytes(B, Hq, T, n_splits)
+    stream = _lib.stream_ptr(dev)
     if ws_bytes:
-        ws = torch.empty(ws_bytes // 4, dtype=torch.float32, device=dev)
+        ws = _lib.workspace(dev, stream, ws_bytes)
     out = torch.empty(B, Hq, T, HEAD_DIM, dtype=torch.float32, device=dev)
     with _lib.on_device(dev):
         _lib.check(lib.omni_qattn_decode_lora(
@@ -140,7 +141,7 @@ def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, w
             _lib.ptr(v_nibbles), _lib.ptr(cb), per_head, _lib.ptr(ids), uid, _lib.ptr(lens), _lib.ptr(slots),
             B, Hq, Hkv, T, S, Hkv * S, S, float(scale), int(bool(with_qjl)), int(bool(rotate_q)),
             int(bool(unrotate_out)), int(n_splits), _lib.ptr(ws), ws_bytes, _lib.ptr(out), _lib.ptr(_lib.status_word(dev)),
-            _lib.stream_ptr(dev), lora_arg))
+            stream, lora_arg))
     return out
 
 

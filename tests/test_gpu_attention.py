@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import oracle as orc
-from tests.helpers import load_golden, t, bf16, sha, config0_inputs
+from tests.helpers import load_golden, t, bf16, sha, config0_inputs, DEFAULT_SCALE
 
 pytestmark = pytest.mark.gpu
 
@@ -250,3 +250,30 @@ def test_lora_prologue_shapes_and_batch_consistency(dev):
         _lib.check_device_status(dev)
     plain = fa.omni_attn(q.to(dev), *cache, user_id=4, scale=0.09)
     assert torch.equal(bad, plain)                        # such rows keep q unchanged
+
+
+def test_dense_anchor_matches_oracle_and_packed_kernel(dev):
+    """``reference_attn`` over dequantised K/V (the reference's numerical anchor, attention/reference.py:72-177)
+    agrees with the oracle's dense attention and with the packed kernel on the same cache."""
+    from omnistack_rs_b200.attention import reference_attn
+    from omnistack_rs_b200.kernels.quantize import dequantize_heads
+    fa = attn_mod()
+    kn, kq, kr, vn, cb, gen = make_cache(2, 2, 200, seed=77, user_id=3)
+    q = torch.randn(2, 8, 3, 128, generator=gen)
+    k_hat = orc.dequantize_heads(kn, kq, kr, cb, 3, True)
+    v_hat = orc.dequantize_heads(vn, kq, kr, cb, 3, False)
+    want = orc.attention(q, k_hat, v_hat, DEFAULT_SCALE)
+    d = to_dev(dev, q, kn, kq, kr, vn, cb)
+    kd = dequantize_heads(d[1], d[2], d[3], d[5], 3, with_qjl=True)
+    vd = dequantize_heads(d[4], d[2], d[3], d[5], 3, with_qjl=False)
+    dense = reference_attn(d[0], kd, vd, tile_size=64)
+    assert dense.dtype == q.dtype and (dense.cpu() - want).abs().max() <= 1e-5
+    packed = fa.omni_attn(*d, user_id=3)
+    assert (packed - dense).abs().max() <= ATOL
+    mask = torch.zeros(2, 8, 3, 200)
+    mask[..., 150:] = float("-inf")
+    masked = reference_attn(d[0], kd, vd, mask=mask.to(dev))
+    short = fa.omni_attn(*d, user_id=3, seq_lens=torch.tensor([150, 150], dtype=torch.int32, device=dev))
+    assert (masked - short).abs().max() <= ATOL
+    with pytest.raises(RuntimeError):
+        reference_attn(q, k_hat, v_hat)
