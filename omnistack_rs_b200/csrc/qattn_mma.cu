@@ -493,6 +493,7 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
             const int64_t qrow_idx = (b * a.Hq + (int64_t)hkv * Gq + cg / a.T) * a.T + (cg % a.T);
             float qv[4];
             Elem<DT>::load4(a.q, qrow_idx * kHeadDim + 4 * lane, qv);
+            if (a.rotate_q) wht128_warp(qv, lane);                  // the rotation folded into the query (fp32, not rounded)
             const float amax = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3]))));
             // fp16 operands stay below 2^10 in magnitude; the power of two is re-applied to the scores
             const float mx = amax * fabsf(qs);
@@ -670,8 +671,8 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int c = 2 * t + j;
-            if (c >= ncols) continue;
-            const int cg = col0 + c;
+            const bool real = c < ncols;                       // every lane runs the shuffles below; only real columns store
+            const int cg = col0 + (real ? c : 0);
             const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + cg / a.T) * a.T + (cg % a.T);
             const float l = j ? st.l1 : st.l0;
             const float m = j ? st.m1 : st.m0;
@@ -684,14 +685,44 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
                 float* w = a.ws + (qrow * a.n_splits + split) * kWsStride;
                 dst = w + 16 * g;
                 mul = 1.f;
-                if (g == 0) { w[128] = m * 0.6931471805599453f; w[129] = l; }   // max back in natural-log units
+                if (real && g == 0) { w[128] = m * 0.6931471805599453f; w[129] = l; }   // max back in natural-log units
             }
+            float v[16];                          // d = 16g + i, i = 4mp + e  (m-tiles 2mp, 2mp+1)
 #pragma unroll
-            for (int mp = 0; mp < 4; ++mp) {      // d = 16g + 4mp .. 16g + 4mp + 3  (m-tiles 2mp, 2mp+1)
-                float4 v;
-                v.x = st.O[2 * mp][j] * mul;     v.y = st.O[2 * mp][2 + j] * mul;
-                v.z = st.O[2 * mp + 1][j] * mul; v.w = st.O[2 * mp + 1][2 + j] * mul;
-                *reinterpret_cast<float4*>(dst + 4 * mp) = v;
+            for (int mp = 0; mp < 4; ++mp) {
+                v[4 * mp] = st.O[2 * mp][j] * mul;         v[4 * mp + 1] = st.O[2 * mp][2 + j] * mul;
+                v[4 * mp + 2] = st.O[2 * mp + 1][j] * mul; v[4 * mp + 3] = st.O[2 * mp + 1][2 + j] * mul;
+            }
+            if (a.unrotate_out && a.n_splits == 1) {
+                // inverse rotation of the finished row (the transform is its own inverse): four stages inside the
+                // thread's 16 dims, three across the eight lanes that share this column (lane bits 2..4 = g)
+#pragma unroll
+                for (int h = 1; h < 16; h <<= 1) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        if ((i & h) == 0) {
+                            const float u = v[i], w2 = v[i | h];
+                            v[i] = u + w2; v[i | h] = u - w2;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int mk = 4; mk <= 16; mk <<= 1) {
+                    const bool lower = (lane & mk) != 0;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float o = __shfl_xor_sync(kFullMask, v[i], mk);
+                        v[i] = lower ? o - v[i] : v[i] + o;
+                    }
+                }
+                const float sc = __uint_as_float(OMNI_WHT_SCALE_BITS);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] *= sc;
+            }
+            if (real) {
+#pragma unroll
+                for (int mp = 0; mp < 4; ++mp)
+                    *reinterpret_cast<float4*>(dst + 4 * mp) = make_float4(v[4 * mp], v[4 * mp + 1], v[4 * mp + 2], v[4 * mp + 3]);
             }
         }
         item = counter ? item_stride + (int64_t)__shfl_sync(kFullMask, ticket, 0) : item + item_stride;
@@ -747,7 +778,7 @@ static int32_t make_nibble_map(CUtensorMap* map, const uint8_t* base) {
 bool mma_eligible(const AttnArgs& a) {
     // any number of query columns per kv head: they are processed in tiles of 8 (one MMA N extent)
     const int64_t cols = (int64_t)(a.Hq / a.Hkv) * a.T;
-    return cols <= 4096 && !a.rotate_q && !a.unrotate_out && a.Hkv <= 65535;
+    return cols <= 4096 && a.Hkv <= 65535;
 }
 
 // Per-device facts that never change while the process lives: looked up once, then read without a driver call.

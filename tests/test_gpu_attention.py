@@ -175,6 +175,14 @@ def test_rotation_folding_and_large_queries(dev):
     folded = fa.omni_attn(q_raw.to(dev), *cache, user_id=1, rotate_q=True, unrotate_out=True).cpu()
     want = orc.wht128(orc.decode_attention(orc.wht128(q_raw), kn, kq, kr, vn, cb, 1))
     assert (folded - want).abs().max() <= ATOL
+    for ns in (2, 5):                                                 # split-K: the merge kernel un-rotates
+        f2 = fa.omni_attn(q_raw.to(dev), *cache, user_id=1, rotate_q=True, unrotate_out=True, n_splits=ns).cpu()
+        assert (f2 - want).abs().max() <= ATOL
+    only_q = fa.omni_attn(q_raw.to(dev), *cache, user_id=1, rotate_q=True).cpu()
+    assert (only_q - orc.decode_attention(orc.wht128(q_raw), kn, kq, kr, vn, cb, 1)).abs().max() <= ATOL
+    q_many = torch.randn(2, 8, 3, 128, generator=gen)                 # 12 query columns per kv head: two column tiles
+    f3 = fa.omni_attn(q_many.to(dev), *cache, user_id=1, rotate_q=True, unrotate_out=True).cpu()
+    assert (f3 - orc.wht128(orc.decode_attention(orc.wht128(q_many), kn, kq, kr, vn, cb, 1))).abs().max() <= ATOL
     # |q| x 200 at S = 512: finite output (reference tests/unit/test_fused_attention.py:256-278)
     big = fa.omni_attn((q_raw * 200).to(dev), *cache, user_id=1).cpu()
     assert torch.isfinite(big).all()
