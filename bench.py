@@ -45,6 +45,8 @@ WORKLOADS = {
     # the reference's own headline benchmark shape (scripts/run_criteo_benchmark.py: 64 users per query, 32 q / 8 kv heads,
     # 50 keys, per-user LoRA query update on, V aliased to K's nibbles); published: 104,571.3 users/s on an A10
     "criteo": ("reference headline shape: 64 users/query, 32 q / 8 kv heads, 50 keys, LoRA-Q on, V = K nibbles", 32, 8, 50, 64),
+    # the other codec kernels, one after the other (reporting only): rotation, dequantisation, fp32 quantize, calibration
+    "codec": ("codec kernels: rotate / dequantize / quantize (fp32, rotated input) / Lloyd-Max fit, 2048 users x 8 heads x 256 tokens", 8, 8, 256, 2048),
     # quantize-append (reporting only): 8 kv heads, 256 new bf16 tokens per user, K and V
     "append": ("config3: 4096 users x 256 new tokens x 8 heads, bf16 K and V, N(0,1) with 1% x10", 8, 8, 256, 4096),
 }
@@ -457,6 +459,70 @@ def run_criteo(args):
     }))
 
 
+def run_codec(args):
+    """Times the codec kernels that no serving workload exercises, each against its algorithmic bytes (single GPU)."""
+    from omnistack_rs_b200 import _lib
+    from omnistack_rs_b200.kernels.hadamard import rotate_queries
+    from omnistack_rs_b200.kernels.quantize import quantize_heads, dequantize_heads
+    from omnistack_rs_b200.quantization import calibrate_per_group
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    desc, _, H, T, users = WORKLOADS["codec"]
+    if args.users:
+        users = args.users
+    rows = users * H * T
+    gen = torch.Generator(device=dev).manual_seed(5)
+    x32 = torch.randn(users, H, T, 128, generator=gen, device=dev)
+    x16 = x32.to(torch.bfloat16)
+    groups = [x32[:, h].reshape(-1)[: 1 << 20].contiguous() for h in range(H)]
+    cb = calibrate_per_group(groups)
+    nib, qjl, nrm = quantize_heads(x32, cb, 3)
+    peak, peak_kind = measured_peak()
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 1)):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / args.steps
+
+    cases = [
+        ("rotate_bf16", lambda: rotate_queries(x16), rows * 512),
+        ("rotate_f32", lambda: rotate_queries(x32), rows * 1024),
+        ("dequantize_int4_qjl", lambda: dequantize_heads(nib, qjl, nrm, cb, 3, with_qjl=True), rows * (76 + 512)),
+        ("dequantize_int4", lambda: dequantize_heads(nib, qjl, nrm, cb, 3, with_qjl=False), rows * (64 + 512)),
+        ("quantize_f32_rotated_input", lambda: quantize_heads(x32, cb, 3), rows * (512 + 76)),
+        ("lloyd_max_fit_8x1M", lambda: calibrate_per_group(groups), H * (1 << 20) * 12),
+    ]
+    kernels = {}
+    for name, fn, nbytes in cases:
+        ms = timed(fn)
+        kernels[name] = {"ms": ms, "gb_per_s": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+    clocks = sampler.stop()
+    _lib.check_device_status(dev)
+    lead = kernels["dequantize_int4_qjl"]
+    print(json.dumps({
+        "metric": "rows_per_sec_dequantize", "value": rows / (lead["ms"] * 1e-3), "unit": "rows/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": lead["ms"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "rows": rows, "l2": "inputs larger than L2 (%.1f GB of fp32 rows)" % (rows * 512 / 1e9),
+                   "note": "timings include the output allocation of the Python API; the Lloyd-Max line includes the sort"},
+        "roofline": {"bound": "hbm", "achieved": lead["gb_per_s"], "peak": peak, "unit": "GB/s", "frac": lead["frac"],
+                     "peak_source": peak_kind, "traffic": None, "kernel": "dequantize_heads_kernel"},
+        "kernels": kernels, "cpu_baseline": None, "e2e": None, "gpu_launches": args.steps, "clocks": clocks,
+    }))
+
+
 def cpu_baseline(Hq, Hkv, S, lens, budget_s=15.0, n_users=2):
     """Time the CPU oracle (port of the reference's torch path) on ``n_users`` users of the
     workload's shape; repeated until about ``budget_s`` seconds have been spent."""
@@ -538,6 +604,8 @@ def main():
         run_append(args)
     elif args.workload == "criteo":
         run_criteo(args)
+    elif args.workload == "codec":
+        run_codec(args)
     else:
         run_ours(args)
 
