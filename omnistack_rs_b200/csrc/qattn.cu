@@ -176,23 +176,54 @@ __global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(Att
     }
 }
 
-// Merge the per-split partial states of one (user, head, token): warp per output row.
-__global__ void __launch_bounds__(kAttnWarps * 32) qattn_combine_kernel(const float* ws, float* out, int64_t n_rows,
-                                                                        int n_splits, int unrotate_out) {
-    const int lane = threadIdx.x & 31;
-    const int64_t r = (int64_t)blockIdx.x * kAttnWarps + (threadIdx.x >> 5);
-    if (r >= n_rows) return;
+// Merge the per-split partial states of one (user, head, token).  A CTA per output row; its warps take the splits
+// round-robin, kCombineUnroll at a time with independent loads (a call with few rows and hundreds of splits is
+// bound by load latency, not by bytes), each keeping a running (max, sum, 128 accumulators) state; the warps' states
+// are merged through shared memory.  Lane l owns dims 4l .. 4l+3.
+constexpr int kCombineWarps = 4;
+constexpr int kCombineUnroll = 4;
+
+__device__ __forceinline__ void merge_state(float& m, float& l, float (&o)[4], float ms, float ls, const float4& v) {
+    const float mn = fmaxf(m, ms);
+    const float fo = (m == -INFINITY) ? 0.f : expf(m - mn);
+    const float fs = (ms == -INFINITY) ? 0.f : expf(ms - mn);
+    l = l * fo + ls * fs;
+    o[0] = o[0] * fo + v.x * fs; o[1] = o[1] * fo + v.y * fs; o[2] = o[2] * fo + v.z * fs; o[3] = o[3] * fo + v.w * fs;
+    m = mn;
+}
+
+__global__ void __launch_bounds__(kCombineWarps * 32) qattn_combine_kernel(const float* ws, float* out, int64_t n_rows,
+                                                                          int n_splits, int unrotate_out) {
+    __shared__ float m_s[kCombineWarps], l_s[kCombineWarps];
+    __shared__ __align__(16) float o_s[kCombineWarps][kHeadDim];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t r = blockIdx.x;
     const float* w = ws + r * n_splits * kWsStride;
-    float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, w[s * kWsStride + 128]);
-    float l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = w[s * kWsStride + 128];
-        const float f = (ms == -INFINITY) ? 0.f : expf(ms - m);
-        l += w[s * kWsStride + 129] * f;
-        const float4 v = *reinterpret_cast<const float4*>(w + s * kWsStride + 4 * lane);
-        o[0] = fmaf(v.x, f, o[0]); o[1] = fmaf(v.y, f, o[1]); o[2] = fmaf(v.z, f, o[2]); o[3] = fmaf(v.w, f, o[3]);
+    float m = -INFINITY, l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s0 = warp; s0 < n_splits; s0 += kCombineWarps * kCombineUnroll) {
+        float ms[kCombineUnroll], ls[kCombineUnroll];
+        float4 v[kCombineUnroll];
+#pragma unroll
+        for (int u = 0; u < kCombineUnroll; ++u) {
+            const int s = s0 + u * kCombineWarps;
+            const bool have = s < n_splits;
+            const float* p = w + (int64_t)(have ? s : s0) * kWsStride;
+            ms[u] = have ? p[128] : -INFINITY;
+            ls[u] = p[129];
+            v[u] = *reinterpret_cast<const float4*>(p + 4 * lane);
+        }
+#pragma unroll
+        for (int u = 0; u < kCombineUnroll; ++u) merge_state(m, l, o, ms[u], ls[u], v[u]);
     }
+    if (lane == 0) { m_s[warp] = m; l_s[warp] = l; }
+    *reinterpret_cast<float4*>(&o_s[warp][4 * lane]) = make_float4(o[0], o[1], o[2], o[3]);
+    __syncthreads();
+    if (warp != 0) return;
+    m = -INFINITY; l = 0.f;
+    o[0] = o[1] = o[2] = o[3] = 0.f;
+#pragma unroll
+    for (int k = 0; k < kCombineWarps; ++k)
+        merge_state(m, l, o, m_s[k], l_s[k], *reinterpret_cast<const float4*>(&o_s[k][4 * lane]));
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int k = 0; k < 4; ++k) o[k] *= inv;
@@ -261,8 +292,8 @@ static int32_t launch(const AttnArgs& a, cudaStream_t st) {
     }
     if (a.n_splits > 1) {
         const int64_t rows = a.B * a.Hq * a.T;
-        qattn_combine_kernel<<<(unsigned)((rows + kAttnWarps - 1) / kAttnWarps), kAttnWarps * 32, 0, st>>>(
-            a.ws, a.out, rows, a.n_splits, a.unrotate_out);
+        OMNI_REQUIRE(rows <= 0x7fffffffLL, OMNI_ERR_UNSUPPORTED, "qattn: %lld output rows exceed one grid", (long long)rows);
+        qattn_combine_kernel<<<(unsigned)rows, kCombineWarps * 32, 0, st>>>(a.ws, a.out, rows, a.n_splits, a.unrotate_out);
         OMNI_CUDA(cudaGetLastError());
     }
     return OMNI_OK;
