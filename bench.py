@@ -54,7 +54,7 @@ BYTES_PER_KEY = 64 + 8 + 4 + 64          # K nibbles + K sign bytes + K norm + V
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per (user, kv head, key) of the decode kernel from the ncu capture summarised in
 # profiles/ (None until a capture exists); scaled to a full launch by the keys it processes.
-NCU_DRAM_BYTES_PER_KEY = 150.2   # profiles/qattn_mma_kernel_serving.md: (10.062 GB read + 0.021 GB written) / 67.1 M keys
+NCU_DRAM_BYTES_PER_KEY = 150.0   # profiles/qattn_mma_kernel_serving.md: (10.048 GB read + 0.020 GB written) / 67.1 M keys
 
 
 def measured_peak():
@@ -248,7 +248,7 @@ def run_ours(args):
     line = {
         "metric": "users_per_sec_quantized_kv_decode", "value": users * world / (ms_step * 1e-3), "unit": "users/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "dtype_note": "f16 tensor-core operands (s8 for the sign term), f32 accumulation and softmax", "data": "synthetic",
         "config": {"workload": desc, "users_per_gpu": users, "resident_users": n_res, "q_heads": Hq, "kv_heads": Hkv,
                    "keys": S, "head_dim": 128, "bytes_per_key": BYTES_PER_KEY, "splits": n_splits,
                    "l2": "inputs larger than L2 (resident cache %.1f GB per GPU)" % (n_res * bytes_per_user / 1e9),
@@ -372,7 +372,7 @@ def run_append(args):
     print(json.dumps({
         "metric": "tokens_per_sec_quantize_append", "value": users * T * world / (ms_step * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "dtype_note": "f32 butterflies and centroid search, s8 tensor-core projections with an exact f64 fallback", "data": "synthetic",
         "config": {"workload": desc, "users_per_gpu": users, "kv_heads": H, "new_tokens": T, "rows_per_step": rows,
                    "l2": "inputs larger than L2" if alg > 2e8 else "inputs smaller than L2"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -446,7 +446,7 @@ def run_criteo(args):
     print(json.dumps({
         "metric": "users_per_sec_quantized_kv_decode", "value": B / (ms * 1e-3), "unit": "users/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": B / (ms * 1e-3) / REFERENCE_A10_USERS_PER_S, "dtype": "f32", "data": "synthetic",
+        "vs_baseline": B / (ms * 1e-3) / REFERENCE_A10_USERS_PER_S, "dtype": "f16", "dtype_note": "f16 tensor-core operands (s8 for the sign term), f32 accumulation and softmax", "data": "synthetic",
         "config": {"workload": desc, "users_per_query": B, "q_heads": Hq, "kv_heads": Hkv, "keys": S, "lora_rank": 16,
                    "l2": "launch-bound case: the 2 MB working set stays in L2 (as in the reference's own run)",
                    "baseline": "104,571.3 users/s on an NVIDIA A10 (reference README.md:83-85)"},
