@@ -437,13 +437,14 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
     const float qs = a.scale * kLog2e;
     bool alive = true;
 
-    // Work distribution.  Every warp starts on item blockIdx.x * kMmaWarps + warp.  Without a counter the next
+    // Work distribution.  Every warp starts on item warp * gridDim.x + blockIdx.x (items go round the CTAs first, so
+    // a call with few items uses one warp on each of many SMs rather than twelve warps on a few).  Without a counter the next
     // item lies one grid of warps further on (equal-sized items: nothing to balance).  With one (split-K calls,
     // whose items differ in length when the users' caches do) a warp takes a ticket for its next item when it
     // starts the current one, so the atomic's latency is covered by the item's own work.
     const int64_t item_stride = (int64_t)gridDim.x * kMmaWarps;
     uint32_t* const counter = a.work_counter ? a.work_counter + blockIdx.y : nullptr;
-    for (int64_t item = (int64_t)blockIdx.x * kMmaWarps + warp; alive && item < n_items;) {
+    for (int64_t item = (int64_t)warp * gridDim.x + blockIdx.x; alive && item < n_items;) {
         uint32_t ticket = 0u;
         if (counter && lane == 0) ticket = atomicAdd(counter, 1u);
         int64_t rest = item;
@@ -830,8 +831,7 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
         ctas = sms;
         gy = 1;
     }
-    const int64_t need = (items + kMmaWarps - 1) / kMmaWarps;
-    if (ctas > need) ctas = need;
+    if (ctas > items) ctas = items;                 // few items: one per CTA, spread over the SMs
     dim3 grid((unsigned)ctas, gy);
     CUtensorMap map_k, map_v;
     rc = make_nibble_map(&map_k, a.k_nib);

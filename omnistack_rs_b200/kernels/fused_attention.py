@@ -18,6 +18,7 @@ Additive keyword arguments: ``seq_lens`` (per-user valid length), ``rotate_q`` /
 from __future__ import annotations
 
 import ctypes as C
+import functools
 import math
 from typing import Optional
 
@@ -86,19 +87,38 @@ def _apply_lora_to_q(q, x, lora_a, lora_b, lora_indices, lora_alpha):
     return out
 
 
+_SPLIT_CANDIDATES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+_WARP_SLOTS = _SM_COUNT * 12
+
+
+@functools.lru_cache(maxsize=4096)
 def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int) -> int:
-    """Key-axis splits from the shape alone (measured on B200, 148 SMs x 12 warps).  A work unit of the
-    tensor-core kernel is one (user, kv head, tile of 8 query columns); a unit costs a fixed prologue, so units
-    are kept at 512 keys or more while there are enough of them (about 12,000: a few per resident warp, which
-    also evens out ragged cache lengths) and shrink to 64 keys only to
-    reach about 1,024 units when the call is small (few users, long caches)."""
+    """Key-axis splits from the shape alone: the candidate with the lowest modelled time.  The model (fitted to a
+    sweep over 1-256 users and 2 K-32 K keys on B200; its pick is within 10 % of the best measured split count
+    for every swept shape): a work unit of the tensor-core kernel - one (user, kv head, tile of 8 query columns,
+    split) - costs about 3 us plus 22 ns per key when it has an SM to itself, rising to 45 ns per key with
+    twelve warps per SM; units run in rounds of 148 x 12; the merge costs 2 us plus its bytes at 1 TB/s."""
     if S < 128 and B * Hq * T < 1024:
         return 1                                   # the lane-per-key kernel's shapes
     units = max(1, B * Hkv * -(-((Hq // Hkv) * T) // 8))
-    splits = max(1, min(-(-12288 // units), S // 512))
-    if units * splits < 1024:
-        splits = max(splits, min(-(-1024 // units), S // 64))
-    return int(max(1, min(splits, 1024)))
+    rows = B * Hq * T
+    best, best_cost, unsplit_cost = 1, float("inf"), float("inf")
+    for s in _SPLIT_CANDIDATES:
+        if s > 1 and S // s < 64:
+            break
+        n = units * s
+        active = min(12.0, max(1.0, n / _SM_COUNT))
+        ns_per_key = 22.0 + 23.0 * (active - 1.0) / 11.0
+        rounds = math.ceil(n / _WARP_SLOTS) if n <= 2 * _WARP_SLOTS else n / _WARP_SLOTS + 0.5
+        cost = rounds * (3.0 + (S / s) * ns_per_key * 1e-3)
+        if s > 1:
+            cost += 2.0 + rows * s * 528 / 1e6
+        if s == 1:
+            unsplit_cost = cost
+        if cost < best_cost:
+            best, best_cost = s, cost
+    # the model is least certain about the fixed cost of a unit on a busy SM: split only for a clear gain
+    return best if best_cost < 0.8 * unsplit_cost else 1
 
 
 def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
