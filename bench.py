@@ -179,7 +179,7 @@ def run_ours(args):
     qs = [torch.randn(users, Hq, 1, 128, device=dev, dtype=torch.bfloat16) for _ in range(n_q)]
 
     from omnistack_rs_b200.kernels.fused_attention import _auto_splits
-    n_splits = args.splits or _auto_splits(users, Hq, Hkv, 1, S)
+    n_splits = args.splits or _auto_splits(users, Hq, Hkv, 1, S, lens is not None)
 
     def step(i):
         return _qattn(qs[i % n_q], k_nib, k_qjl, k_norms, v_nib, cb, 0, scale, True,

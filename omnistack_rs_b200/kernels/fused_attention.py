@@ -92,12 +92,14 @@ _WARP_SLOTS = _SM_COUNT * 12
 
 
 @functools.lru_cache(maxsize=4096)
-def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int) -> int:
+def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int, ragged: bool = False) -> int:
     """Key-axis splits from the shape alone: the candidate with the lowest modelled time.  The model (fitted to a
     sweep over 1-256 users and 2 K-32 K keys on B200; its pick is within 10 % of the best measured split count
     for every swept shape): a work unit of the tensor-core kernel - one (user, kv head, tile of 8 query columns,
     split) - costs about 3 us plus 22 ns per key when it has an SM to itself, rising to 45 ns per key with
-    twelve warps per SM; units run in rounds of 148 x 12; the merge costs 2 us plus its bytes at 1 TB/s."""
+    twelve warps per SM; units run in rounds of 148 x 12; the merge costs 2 us plus its bytes at 1 TB/s.
+    ``ragged`` (per-user cache lengths were given): at least 8 splits of 512 keys or more, so that the ticket
+    scheduling can even the lengths out, unless every warp has many units anyway."""
     if S < 128 and B * Hq * T < 1024:
         return 1                                   # the lane-per-key kernel's shapes
     units = max(1, B * Hkv * -(-((Hq // Hkv) * T) // 8))
@@ -118,7 +120,11 @@ def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int) -> int:
         if cost < best_cost:
             best, best_cost = s, cost
     # the model is least certain about the fixed cost of a unit on a busy SM: split only for a clear gain
-    return best if best_cost < 0.8 * unsplit_cost else 1
+    if best_cost >= 0.8 * unsplit_cost:
+        best = 1
+    if ragged and units < 8 * _WARP_SLOTS:
+        best = max(best, min(8, S // 512))
+    return best
 
 
 def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
@@ -144,7 +150,7 @@ def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, w
     lens = None if seq_lens is None else _lib.as_device(seq_lens, dev, torch.int32)
     slots = None if cache_slots is None else _lib.as_device(cache_slots, dev, torch.int32)
     if n_splits is None:
-        n_splits = _auto_splits(B, Hq, Hkv, T, S)
+        n_splits = _auto_splits(B, Hq, Hkv, T, S, seq_lens is not None)
     ws, ws_bytes, lora_arg = None, 0, None
     if lora is not None:
         x, la, lb, idx = _prep_lora(q, lora[0], lora[1], lora[2], lora[3], dev)

@@ -130,7 +130,7 @@ class HostDecodeStep:
             n_chunks = max(1, min(8, batch // 2048))
         self.with_qjl, self.n_chunks = int(bool(with_qjl)), int(n_chunks)
         per_chunk = -(-batch // self.n_chunks)
-        self.n_splits = int(n_splits) if n_splits is not None else _auto_splits(per_chunk, n_heads, self.Hkv, T, self.S)
+        self.n_splits = int(n_splits) if n_splits is not None else _auto_splits(per_chunk, n_heads, self.Hkv, T, self.S, seq_lens is not None)
         self.ws_bytes = 2 * self.lib.omni_qattn_workspace_bytes(per_chunk, n_heads, T, self.n_splits)
         self.ws = torch.empty(max(self.ws_bytes // 4, 1), dtype=torch.float32, device=self.dev)
         shape = (batch, n_heads, T, HEAD_DIM)
