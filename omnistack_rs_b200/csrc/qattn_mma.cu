@@ -405,9 +405,10 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
     {
         const float* cb = a.codebooks + (a.cb_per_head ? cb_head * 16 : 0);
         uint32_t* lut = reinterpret_cast<uint32_t*>(smem + lut_off);
-        for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
-            const int byte = i >> 5, ln = i & 31;
-            lut[byte * 64 + ln] = pack_half2(__ldg(cb + (byte & 15)), __ldg(cb + (byte >> 4)));
+        for (int i = threadIdx.x; i < 256 * 8; i += blockDim.x) {       // four lanes' copies of an entry per store
+            const int byte = i >> 3, quad = i & 7;
+            const uint32_t v = pack_half2(__ldg(cb + (byte & 15)), __ldg(cb + (byte >> 4)));
+            *reinterpret_cast<uint4*>(lut + byte * 64 + 4 * quad) = make_uint4(v, v, v, v);
         }
     }
     const uint32_t lut_lane = smem_base + lut_off + 4 * lane;                  // bits 8..15 are zero
@@ -762,7 +763,31 @@ static EncodeTiledFn encode_tiled_fn() {
 // 2-D view [rows][64 bytes] of a nibble array with a kStageKeys-row box and the 64-byte swizzle.  The row
 // extent is the largest a 32-bit row coordinate can address: only full kStageKeys-row boxes that lie inside
 // the caller's arrays are ever requested, so nothing depends on out-of-bounds clipping.
+// The descriptor depends on the base address alone, so the last few are kept: a serving loop calls with the same
+// cache arrays every step and skips the driver call.
+struct MapCacheEntry { const uint8_t* base; CUtensorMap map; };
+constexpr int kMapCacheSize = 8;
+static MapCacheEntry g_map_cache[kMapCacheSize];
+static int g_map_cache_next = 0;
+static std::mutex g_map_cache_mutex;
+
+static int32_t encode_nibble_map(CUtensorMap* map, const uint8_t* base);
+
 static int32_t make_nibble_map(CUtensorMap* map, const uint8_t* base) {
+    {
+        std::lock_guard<std::mutex> lk(g_map_cache_mutex);
+        for (int i = 0; i < kMapCacheSize; ++i)
+            if (g_map_cache[i].base == base && base != nullptr) { *map = g_map_cache[i].map; return OMNI_OK; }
+    }
+    const int32_t rc = encode_nibble_map(map, base);
+    if (rc != OMNI_OK) return rc;
+    std::lock_guard<std::mutex> lk(g_map_cache_mutex);
+    g_map_cache[g_map_cache_next] = MapCacheEntry{base, *map};
+    g_map_cache_next = (g_map_cache_next + 1) % kMapCacheSize;
+    return OMNI_OK;
+}
+
+static int32_t encode_nibble_map(CUtensorMap* map, const uint8_t* base) {
     EncodeTiledFn fn = encode_tiled_fn();
     OMNI_REQUIRE(fn != nullptr, OMNI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[2] = {(cuuint64_t)kNibBytes, (cuuint64_t)0x7fffffffull};
