@@ -17,6 +17,9 @@
 //     few projections inside that band are recomputed exactly in fp64;
 //   * packed outputs: 16-byte nibble stores per lane (64 contiguous bytes per row), 2-byte sign stores.
 #include "codec_fast.cuh"
+#include <mutex>
+#include <utility>
+#include <vector>
 
 namespace omni {
 
@@ -573,7 +576,20 @@ static int32_t launch_fast_t(const FastQuantArgs& a, int rotate, cudaStream_t st
     int64_t blocks = (pairs + kFqWarps - 1) / kFqWarps;
     if (blocks > 2 * sms) blocks = 2 * sms;
     auto kern = rotate ? fast_quantize_kernel<DT, true> : fast_quantize_kernel<DT, false>;
-    OMNI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    {   // opt in once per (kernel, device) to the shared memory of the largest table count the kernel accepts
+        static std::mutex mu;
+        static std::vector<std::pair<const void*, int>> done;
+        const void* key = reinterpret_cast<const void*>(kern);
+        std::lock_guard<std::mutex> lk(mu);
+        bool seen = false;
+        for (const auto& p : done) seen = seen || (p.first == key && p.second == dev);
+        if (!seen) {
+            const size_t smem_max = sizeof(HeadTables) * kFqMaxHeads + (size_t)kFqWarps * 16 * 32 * sizeof(uint4) +
+                                    (size_t)kFqWarps * kStageBytesPerWarp;
+            OMNI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
+            done.emplace_back(key, dev);
+        }
+    }
     kern<<<(unsigned)blocks, kFqWarps * 32, smem, st>>>(a);
     return check_cuda(cudaGetLastError(), "fast_quantize_kernel launch");
 }
