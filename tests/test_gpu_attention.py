@@ -260,6 +260,18 @@ def test_lora_prologue_shapes_and_batch_consistency(dev):
     assert torch.equal(bad, plain)                        # such rows keep q unchanged
 
 
+@pytest.mark.parametrize("n_splits", [16, 37, 200, None])
+def test_single_user_long_cache_many_splits(dev, n_splits):
+    """One user, 32 q / 8 kv heads, 6,000 keys: far more key splits than resident warps need, odd split counts,
+    splits of fewer keys than a stage, and the split count the library picks by itself."""
+    fa = attn_mod()
+    kn, kq, kr, vn, cb, gen = make_cache(1, 8, 6000, seed=88, user_id=7, per_head=False)
+    q = torch.randn(1, 32, 1, 128, generator=gen).to(torch.bfloat16)
+    want = orc.decode_attention(q, kn, kq, kr, vn, cb, 7)
+    out = fa.omni_attn(*to_dev(dev, q, kn, kq, kr, vn, cb), user_id=7, n_splits=n_splits).cpu()
+    assert (out - want).abs().max() <= ATOL
+
+
 def test_dense_anchor_matches_oracle_and_packed_kernel(dev):
     """``reference_attn`` over dequantised K/V (the reference's numerical anchor, attention/reference.py:72-177)
     agrees with the oracle's dense attention and with the packed kernel on the same cache."""
