@@ -52,9 +52,9 @@ WORKLOADS = {
 }
 BYTES_PER_KEY = 64 + 8 + 4 + 64          # K nibbles + K sign bytes + K norm + V nibbles
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per (user, kv head, key) of the decode kernel from the ncu capture summarised in
-# profiles/ (None until a capture exists); scaled to a full launch by the keys it processes.
-NCU_DRAM_BYTES_PER_KEY = 150.0   # profiles/qattn_mma_kernel_serving.md: (10.048 GB read + 0.020 GB written) / 67.1 M keys
+# DRAM bytes per (user, kv head, key) of the decode kernel from its committed ncu capture summary;
+# scaled to a full launch by the keys it processes.
+NCU_DRAM_BYTES_PER_KEY = 150.0   # ncu capture of the decode kernel: (10.048 GB read + 0.020 GB written) / 67.1 M keys
 
 
 def measured_peak():
