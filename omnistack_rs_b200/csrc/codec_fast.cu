@@ -30,12 +30,11 @@ constexpr int kFqMaxHeads = 32;
 struct HeadTables {
     float thr[20];          // thr[c], c = 1..15: smallest fp32 y whose code is >= c; thr[16] = +inf
     float cb[16];
-    uint8_t cell[32];       // code at the low end of each grid cell
+    float2 cell2[32];       // per grid cell: x = threshold between the cell's two codes, y = the lower code (int bits)
     float inv32, off32;     // cell(y) = rn(31 * sat(y * inv32 + off32))
     float guard;            // |y| <= guard: the threshold shortcut is valid
     int valid;              // 0: this codebook always takes the defining scan; 1: grid cell + one compare;
                             // 2: binary search over the 15 exact thresholds (the grid cannot resolve them)
-    int pad[4];
 };
 static_assert(sizeof(HeadTables) % 16 == 0, "HeadTables must keep 16-byte alignment in an array");
 
@@ -118,7 +117,7 @@ __device__ void build_head_tables(HeadTables& ht, const float* cb_global, int la
     const int top = code_by_scan(b, ht.cb);
     ok = __all_sync(kFullMask, top - base <= 1 && top >= base) &&
          cell_of(-guard, inv32, off32) == 0 && cell_of(guard, inv32, off32) == 31;
-    ht.cell[lane] = (uint8_t)base;
+    ht.cell2[lane] = make_float2(ht.thr[base + 1], __int_as_float(base));
     // A grid that cannot separate the thresholds (two of them in one cell) leaves the exact thresholds usable
     // by themselves: such codebooks take the four-step binary search, for every finite y.
     if (lane == 0) { ht.valid = ok ? 1 : 2; ht.guard = ok ? guard : 3.0e38f; ht.inv32 = inv32; ht.off32 = off32; }
@@ -395,8 +394,8 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
             } else {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const int base = ht.cell[cell_of(y[i], inv32, off32)];
-                    const int c = base + (y[i] >= ht.thr[base + 1] ? 1 : 0);
+                    const float2 rec = ht.cell2[cell_of(y[i], inv32, off32)];
+                    const int c = __float_as_int(rec.y) + (y[i] >= rec.x ? 1 : 0);
                     codes[i >> 3] |= (uint32_t)c << (4 * (i & 7));
                     y[i] = __fsub_rn(y[i], ht.cb[c]);
                 }
