@@ -169,8 +169,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) dequantize_kernel(CodecAr
 // Head-seeded dequantisation, the streaming form: a warp takes a run of consecutive tokens of one (user, head), so
 // the head's 16 centroids (one per lane, fetched by shuffle) and this lane's four columns of G stay in registers
 // for the whole run; per token it reads 2 bytes of codes per lane plus the broadcast sign word and norm, and
-// writes 16 bytes per lane.  Two tokens are in flight per iteration.
+// writes 16 bytes per lane.  kDeqFlight tokens are in flight per iteration.
 constexpr int kDeqRun = 64;     // tokens per work unit
+constexpr int kDeqFlight = 4;   // tokens whose loads are issued together
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) dequantize_heads_kernel(CodecArgs a) {
     const int lane = threadIdx.x & 31;
@@ -191,35 +192,35 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) dequantize_heads_kernel(C
         }
         const int64_t t_begin = run * kDeqRun, t_end = (t_begin + kDeqRun < a.T) ? t_begin + kDeqRun : a.T;
         const int64_t in0 = b * a.os_b + h * a.os_h, out0 = (b * a.H + h) * a.T;
-        for (int64_t t = t_begin; t < t_end; t += 2) {
-            const bool two = t + 1 < t_end;
-            const int64_t r0 = in0 + t, r1 = in0 + (two ? t + 1 : t);
-            const uint32_t p0 = reinterpret_cast<const uint16_t*>(a.nib + r0 * kNibBytes)[lane];
-            const uint32_t p1 = reinterpret_cast<const uint16_t*>(a.nib + r1 * kNibBytes)[lane];
-            uint2 s0 = make_uint2(0u, 0u), s1 = make_uint2(0u, 0u);
-            float c0 = 0.f, c1 = 0.f;
-            if (a.with_qjl) {
-                s0 = *reinterpret_cast<const uint2*>(a.qjl + r0 * kQjlBytes);
-                s1 = *reinterpret_cast<const uint2*>(a.qjl + r1 * kQjlBytes);
-                c0 = __fmul_rn(a.norms[r0], kQjlCoef);
-                c1 = __fmul_rn(a.norms[r1], kQjlCoef);
-            }
-            float v0[4], v1[4];
+        for (int64_t t = t_begin; t < t_end; t += kDeqFlight) {
+            uint32_t p[kDeqFlight];
+            uint2 sg[kDeqFlight];
+            float cf[kDeqFlight];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                v0[k] = __shfl_sync(kFullMask, cb_lane, (p0 >> (4 * k)) & 0xF);
-                v1[k] = __shfl_sync(kFullMask, cb_lane, (p1 >> (4 * k)) & 0xF);
-            }
-            if (a.with_qjl) {
-                const uint64_t sig0 = ((uint64_t)s0.y << 32) | s0.x, sig1 = ((uint64_t)s1.y << 32) | s1.x;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {       // sum_i s_i * g_id with s, g in {-1,+1}: matches minus mismatches
-                    v0[k] = __fadd_rn(v0[k], __fmul_rn((float)(kQjlDim - 2 * __popcll(sig0 ^ gc[k])), c0));
-                    v1[k] = __fadd_rn(v1[k], __fmul_rn((float)(kQjlDim - 2 * __popcll(sig1 ^ gc[k])), c1));
+            for (int u = 0; u < kDeqFlight; ++u) {             // all loads of the batch first
+                const int64_t r = in0 + (t + u < t_end ? t + u : t_end - 1);
+                p[u] = reinterpret_cast<const uint16_t*>(a.nib + r * kNibBytes)[lane];
+                sg[u] = make_uint2(0u, 0u);
+                cf[u] = 0.f;
+                if (a.with_qjl) {
+                    sg[u] = *reinterpret_cast<const uint2*>(a.qjl + r * kQjlBytes);
+                    cf[u] = __fmul_rn(a.norms[r], kQjlCoef);
                 }
             }
-            *reinterpret_cast<float4*>(a.out + (out0 + t) * kHeadDim + 4 * lane) = make_float4(v0[0], v0[1], v0[2], v0[3]);
-            if (two) *reinterpret_cast<float4*>(a.out + (out0 + t + 1) * kHeadDim + 4 * lane) = make_float4(v1[0], v1[1], v1[2], v1[3]);
+#pragma unroll
+            for (int u = 0; u < kDeqFlight; ++u) {
+                float v[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v[k] = __shfl_sync(kFullMask, cb_lane, (p[u] >> (4 * k)) & 0xF);
+                if (a.with_qjl) {
+                    const uint64_t sig = ((uint64_t)sg[u].y << 32) | sg[u].x;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)         // sum_i s_i * g_id with s, g in {-1,+1}: matches minus mismatches
+                        v[k] = __fadd_rn(v[k], __fmul_rn((float)(kQjlDim - 2 * __popcll(sig ^ gc[k])), cf[u]));
+                }
+                if (t + u < t_end)
+                    *reinterpret_cast<float4*>(a.out + (out0 + t + u) * kHeadDim + 4 * lane) = make_float4(v[0], v[1], v[2], v[3]);
+            }
         }
     }
 }
