@@ -139,34 +139,73 @@ def build_resident_cache(dev, Hkv, S, n_res, seed, lens=None):
     return k_nib, k_qjl, k_norms, v_nib, cb
 
 
-def run_ours(args):
+def decode_launches_per_step(users, Hq, T, S, n_splits):
+    """Kernels one decode call launches: the tensor-core kernel and its fp32 stand-by (or the lane-per-key kernel
+    alone for small shapes), plus the split-K merge."""
+    mma = S >= 128 or users * Hq * T >= 1024
+    return (2 if mma else 1) + (1 if n_splits > 1 else 0)
+
+
+def verify_against_oracle(dev, rank, world, users, Hq, q, out, k_nib, k_qjl, k_norms, v_nib, cb, slots, lens, n_check=4):
+    """Scores gathered to rank 0 for verification (NCCL when there are several ranks): one checksum row per user
+    and, for ``n_check`` sampled users of every rank, the full output rows together with the packed cache rows and
+    the query they were computed from; rank 0 recomputes those users with the CPU oracle."""
+    import torch.distributed as dist
+    from omnistack_rs_b200.serving import gather_rows_to_rank0
+    g = torch.Generator().manual_seed(100 + rank)
+    picks = sorted({0, users - 1, *torch.randint(0, users, (max(n_check - 2, 0),), generator=g).tolist()})
+    while len(picks) < min(n_check, users):
+        picks.append(next(u for u in range(users) if u not in picks))
+    picks = sorted(picks)[:n_check]
+    idx = torch.tensor(picks, device=dev)
+    slot = idx if slots is None else slots[idx].long()
+    S = k_nib.shape[2]
+    sample = {"out": out[idx].float(), "q": q[idx], "kn": k_nib[slot], "kq": k_qjl[slot],
+              "kr": k_norms[slot], "vn": v_nib[slot],
+              "len": (lens[idx].to(torch.int32) if lens is not None else torch.full((len(picks),), S, dtype=torch.int32, device=dev))}
+    checksum = out.float().sum(dim=(1, 2, 3)).unsqueeze(1)                      # one number per user
+    if world > 1:
+        sample = {k: gather_rows_to_rank0(v.contiguous(), len(picks) * world) for k, v in sample.items()}
+        checksum = gather_rows_to_rank0(checksum.contiguous(), users * world)
+    if rank != 0:
+        return None
+    import oracle as orc
+    use_all_host_threads()
+    cbc = cb.cpu()
+    worst = 0.0
+    for i in range(sample["out"].shape[0]):
+        n = int(sample["len"][i])
+        if n == 0:
+            continue
+        want = orc.decode_attention(sample["q"][i:i + 1].cpu(), sample["kn"][i:i + 1, :, :n].cpu(),
+                                    sample["kq"][i:i + 1, :, :n].cpu(), sample["kr"][i:i + 1, :, :n].cpu(),
+                                    sample["vn"][i:i + 1, :, :n].cpu(), cbc, 0)
+        worst = max(worst, float((sample["out"][i:i + 1].cpu() - want).abs().max()))
+    return {"users_checked": int(sample["out"].shape[0]), "max_abs_err": worst, "tolerance": 3e-3,
+            "ok": bool(worst <= 3e-3 and torch.isfinite(checksum).all()), "ranks": world,
+            "checksum_rows_gathered": int(checksum.shape[0]), "transport": "nccl gather" if world > 1 else "local"}
+
+
+def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_cpu, with_verify):
+    """Times one decode workload on this rank's GPU; returns the fields of its JSON line (rank 0) or None."""
     import torch.distributed as dist
     from omnistack_rs_b200 import _lib
-    from omnistack_rs_b200.kernels.fused_attention import _qattn
+    from omnistack_rs_b200.kernels.fused_attention import _qattn, _auto_splits
     from omnistack_rs_b200.serving import HostDecodeStep
 
-    rank, world, local = dist_env()
-    if args.gpus != world and world > 1:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    desc, Hq, Hkv, S, users = WORKLOADS[args.workload]
-    if args.users:
+    desc, Hq, Hkv, S, users = WORKLOADS[workload]
+    if args.users and workload == args.workload:
         users = args.users
     scale = 1.0 / math.sqrt(128)
 
     # ---- resident cache ------------------------------------------------------------
     bytes_per_user = Hkv * S * BYTES_PER_KEY
     free, _total = torch.cuda.mem_get_info(dev)
-    budget = free - (20 << 30) if args.resident_users is None else None
-    n_res = args.resident_users or max(1, min(users, budget // bytes_per_user))
+    budget = free - (20 << 30)
+    n_res = (args.resident_users if workload == args.workload else None) or max(1, min(users, budget // bytes_per_user))
     n_res = min(n_res, users)
     lens = None
-    if args.workload == "gqa":
+    if workload == "gqa":
         g = torch.Generator().manual_seed(1)
         lens = torch.randint(1024, 8193, (users,), generator=g).to(torch.int32)
     k_nib, k_qjl, k_norms, v_nib, cb = build_resident_cache(dev, Hkv, S, n_res, seed=1234 + rank)
@@ -177,9 +216,7 @@ def run_ours(args):
 
     n_q = 4
     qs = [torch.randn(users, Hq, 1, 128, device=dev, dtype=torch.bfloat16) for _ in range(n_q)]
-
-    from omnistack_rs_b200.kernels.fused_attention import _auto_splits
-    n_splits = args.splits or _auto_splits(users, Hq, Hkv, 1, S, lens is not None)
+    n_splits = (args.splits if workload == args.workload else None) or _auto_splits(users, Hq, Hkv, 1, S, lens is not None)
 
     def step(i):
         return _qattn(qs[i % n_q], k_nib, k_qjl, k_norms, v_nib, cb, 0, scale, True,
@@ -190,37 +227,55 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    # A working set smaller than L2 (the 64-user configuration) is flushed between timed steps by writing a
+    # buffer larger than L2; the larger workloads stream far more than L2 holds per step.
+    small = alg_bytes < (256 << 20)
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev) if small else None
+
     # ---- device-resident timing ------------------------------------------------------
-    for i in range(args.warmup):
+    for i in range(warmup):
         step(i)
     barrier()
     sampler = ClockSampler(local)
     sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(args.steps):
-        out = step(i)
-    ev1.record()
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
+    if small:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for i, (e0, e1) in enumerate(evs):
+            flush.fill_(i & 1)
+            e0.record()
+            out = step(i)
+            e1.record()
+        barrier()
+        ms_total = sum(e0.elapsed_time(e1) for e0, e1 in evs)
+    else:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(steps):
+            out = step(i)
+        ev1.record()
+        barrier()
+        ms_total = ev0.elapsed_time(ev1)
     clocks = sampler.stop()
     tmax = torch.tensor([ms_total], device=dev)
     if world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    ms_step = float(tmax) / args.steps
-    launches_per_step = 1 if n_splits == 1 else 2
+    ms_step = float(tmax) / steps
+    launches = decode_launches_per_step(users, Hq, 1, S, n_splits)
     checksum = float(out.float().abs().mean())
 
     # ---- end to end: host query in, host result out -----------------------------------
     host = HostDecodeStep(k_nib, k_qjl, k_norms, v_nib, cb, n_heads=Hq, batch=users, q_dtype=torch.bfloat16,
-                          user_id=0, seq_lens=lens_dev, cache_slots=slots, scale=scale, n_chunks=args.chunks)
+                          user_id=0, seq_lens=lens_dev, cache_slots=slots, scale=scale,
+                          n_chunks=args.chunks if workload == args.workload else None)
     host.q_host.copy_(qs[0].cpu())
-    for _ in range(max(1, min(args.warmup, 3))):
+    for _ in range(max(1, min(warmup, 3))):
         host.step()
     barrier()
-    e2e_steps = args.steps
+    e2e_steps = steps
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
+        if small:
+            flush.fill_(1)
         res = host.step()
     torch.cuda.synchronize(dev)
     t1 = time.perf_counter()
@@ -229,43 +284,80 @@ def run_ours(args):
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_s_step = float(e2e_t) / e2e_steps
     ref_out = _qattn(qs[0], k_nib, k_qjl, k_norms, v_nib, cb, 0, scale, True,
-                     seq_lens=lens_dev, cache_slots=slots, n_splits=1).cpu()
-    e2e_ok = bool((res - ref_out).abs().max() <= 1e-4)     # split / chunk boundaries may differ in the last bits
+                     seq_lens=lens_dev, cache_slots=slots, n_splits=1)
+    e2e_ok = bool((res - ref_out.cpu()).abs().max() <= 1e-4)     # split / chunk boundaries may differ in the last bits
     _lib.check_device_status(dev)
+
+    verify = None
+    if with_verify:
+        verify = verify_against_oracle(dev, rank, world, users, Hq, qs[0], ref_out, k_nib, k_qjl, k_norms, v_nib, cb,
+                                       slots, lens_dev)
 
     # ---- CPU baseline: the oracle on a few users of the same shape (rank 0, N = 1) ------
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if with_cpu and rank == 0 and world == 1:
         cpu = cpu_baseline(Hq, Hkv, S, lens, budget_s=args.cpu_seconds)
-
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
     if rank != 0:
-        return
+        return None
     peak, peak_kind = measured_peak()
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
-    line = {
+    return {
         "metric": "users_per_sec_quantized_kv_decode", "value": users * world / (ms_step * 1e-3), "unit": "users/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "dtype_note": "f16 tensor-core operands (s8 for the sign term), f32 accumulation and softmax", "data": "synthetic",
         "config": {"workload": desc, "users_per_gpu": users, "resident_users": n_res, "q_heads": Hq, "kv_heads": Hkv,
                    "keys": S, "head_dim": 128, "bytes_per_key": BYTES_PER_KEY, "splits": n_splits,
-                   "l2": "inputs larger than L2 (resident cache %.1f GB per GPU)" % (n_res * bytes_per_user / 1e9),
+                   "l2": ("L2 flushed between timed steps (a 192 MiB buffer is written before each)" if small else
+                          "inputs larger than L2 (resident cache %.1f GB per GPU)" % (n_res * bytes_per_user / 1e9)),
                    "parallelism": f"users sharded over {world} GPU(s), no collective on the data path"},
         "kv_gb_per_s": achieved * world,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_kind, "frac_of_8000_nominal": achieved / 8000.0,
                      "traffic": (NCU_DRAM_BYTES_PER_KEY * keys_per_step if NCU_DRAM_BYTES_PER_KEY else None),
-                     "algorithmic_bytes_per_launch": alg_bytes, "kernel": "qattn decode", "launch_ms": ms_step / launches_per_step},
+                     "algorithmic_bytes_per_launch": alg_bytes, "kernel": "qattn decode", "launch_ms": ms_step},
         "cpu_baseline": cpu,
         "e2e": {"value": users * world / e2e_s_step, "unit": "users/s", "h2d_bytes_per_step": host.h2d_bytes,
                 "d2h_bytes_per_step": host.d2h_bytes, "ms_per_step": e2e_s_step * 1e3, "chunks": host.n_chunks, "splits": host.n_splits,
                 "matches_device_path": e2e_ok},
-        "gpu_launches": args.steps * launches_per_step,
+        "verify": verify,
+        "gpu_launches": steps * launches,
         "clocks": clocks, "checksum": checksum,
     }
-    print(json.dumps(line))
+
+
+SECONDARY_KEYS = ("value", "unit", "ms_per_step", "steps", "e2e", "clocks", "config")
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    rank, world, local = dist_env()
+    if args.gpus != world and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    line = measure_decode(args, args.workload, dev, rank, world, local, args.steps, args.warmup,
+                          with_cpu=not args.no_cpu, with_verify=not args.no_verify)
+    # The other benchmark configurations, measured in the same process once the headline cache is freed
+    # (single-GPU runs of the default workload only; each is also a workload of its own via --workload).
+    if world == 1 and args.workload == "serve" and not args.no_secondary:
+        secondary = {}
+        torch.cuda.empty_cache()
+        for name, wl, st in (("config1_decode64", "decode64", 200), ("config2_gqa", "gqa", 50)):
+            r = measure_decode(args, wl, dev, rank, world, local, st, 5, with_cpu=False, with_verify=True)
+            torch.cuda.empty_cache()
+            secondary[name] = {k: r[k] for k in SECONDARY_KEYS} | {"roofline": r["roofline"], "verify": r["verify"]}
+        r = measure_append(args, dev, rank, world, local, 20, 5, with_cpu=False)
+        secondary["config3_append"] = {k: r[k] for k in SECONDARY_KEYS} | {"roofline": r["roofline"]}
+        line["secondary"] = secondary
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
 
 
 def use_all_host_threads():
@@ -279,20 +371,27 @@ def use_all_host_threads():
 
 
 def run_append(args):
-    """Quantize-append workload (benchmark configuration 3): every step rotates and quantizes 256 new
-    bf16 K and V tokens per user into the users' packed caches.  Metric: tokens/s."""
     import torch.distributed as dist
-    import oracle as orc
-    from omnistack_rs_b200 import _lib
-    from omnistack_rs_b200.kernels.quantize import _quantize_into
-
     rank, world, local = dist_env()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    line = measure_append(args, dev, rank, world, local, args.steps, args.warmup, with_cpu=not args.no_cpu)
+    if world > 1:
+        dist.barrier(); dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+def measure_append(args, dev, rank, world, local, steps, warmup, with_cpu):
+    """Quantize-append workload (benchmark configuration 3): every step rotates and quantizes 256 new
+    bf16 K and V tokens per user into the users' packed caches.  Metric: tokens/s."""
+    import torch.distributed as dist
+    from omnistack_rs_b200.kernels.quantize import _quantize_into
+
     desc, _, H, T, users = WORKLOADS["append"]
-    if args.users:
+    if args.users and args.workload == "append":
         users = args.users
     gen = torch.Generator(device=dev).manual_seed(99 + rank)
 
@@ -317,14 +416,14 @@ def run_append(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step(xk, xv)
     barrier()
     sampler = ClockSampler(local)
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step(xk, xv)
     ev1.record()
     barrier()
@@ -332,11 +431,11 @@ def run_append(args):
     tmax = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
     if world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    ms_step = float(tmax) / args.steps
+    ms_step = float(tmax) / steps
     # end to end: new tokens arrive in pinned host memory; a checksum of the norms goes back
     hk, hv = xk.cpu().pin_memory(), xv.cpu().pin_memory()
     dk, dv = torch.empty_like(xk), torch.empty_like(xv)
-    e2e_steps = max(1, min(args.steps, 5))
+    e2e_steps = max(1, min(steps, 5))
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
@@ -349,7 +448,8 @@ def run_append(args):
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and with_cpu:
+        import oracle as orc
         use_all_host_threads()
         n = 16
         xs = xk[:n].cpu()
@@ -361,17 +461,15 @@ def run_append(args):
         cpu = {"value": n * T / dt / 1.0, "unit": "tokens/s", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
                "kind": "port", "sample": f"{n} users x {H} heads x {T} tokens, K only, CPU oracle (rotate + quantize_heads)"}
         cpu["value"] = cpu["value"] / 2.0      # a token is a K row and a V row per head
-    if world > 1:
-        dist.barrier(); dist.destroy_process_group()
     if rank != 0:
-        return
+        return None
     peak, peak_kind = measured_peak()
     rows = 2 * users * H * T
     alg = rows * (256 + 76)
     achieved = alg / (ms_step * 1e-3) / 1e9
-    print(json.dumps({
+    return {
         "metric": "tokens_per_sec_quantize_append", "value": users * T * world / (ms_step * 1e-3), "unit": "tokens/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "dtype_note": "f32 butterflies and centroid search, s8 tensor-core projections with an exact f64 fallback", "data": "synthetic",
         "config": {"workload": desc, "users_per_gpu": users, "kv_heads": H, "new_tokens": T, "rows_per_step": rows,
                    "l2": "inputs larger than L2" if alg > 2e8 else "inputs smaller than L2"},
@@ -381,8 +479,8 @@ def run_append(args):
         "cpu_baseline": cpu,
         "e2e": {"value": users * T * world / float(e2e_t), "unit": "tokens/s", "h2d_bytes_per_step": 2 * hk.numel() * 2,
                 "d2h_bytes_per_step": 4, "ms_per_step": float(e2e_t) * 1e3},
-        "gpu_launches": 2 * args.steps, "clocks": clocks, "checksum": chk,
-    }))
+        "gpu_launches": 2 * steps, "clocks": clocks, "checksum": chk,
+    }
 
 
 REFERENCE_A10_USERS_PER_S = 104571.3      # README.md:83-85 of the reference (A10, the shape of the "criteo" workload)
@@ -593,6 +691,8 @@ def main():
     ap.add_argument("--splits", type=int, default=None, help="key-axis splits (default: chosen from the shape)")
     ap.add_argument("--chunks", type=int, default=None, help="user chunks of the pipelined host-buffer step (default: by batch)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-verify", action="store_true", help="skip the oracle check of gathered sample users")
+    ap.add_argument("--no-secondary", action="store_true", help="default workload only: skip the other configurations")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--ref-users", type=int, default=2, help="users per step of the reference arm")
     args = ap.parse_args()

@@ -47,6 +47,7 @@ extern "C" {
 /* values a kernel may leave in a caller's device status word (0 = nothing to report) */
 #define OMNI_STATUS_WAIT_EXPIRED  4   /* a bounded device-side wait ran out                      */
 #define OMNI_STATUS_BAD_INDEX     7   /* an adapter index was at or past the adapter count       */
+#define OMNI_STATUS_BAD_CODEBOOK  8   /* an attention call was given an infinite or NaN centroid */
 
 /* element types of floating-point inputs */
 #define OMNI_F32   0
@@ -81,7 +82,9 @@ int32_t omni_rotate(const void* x, void* y, int64_t n_rows, int32_t dtype, void*
  *   nib/qjl/norms device outputs; row index of (b,h,t) is
  *                b*os_b + h*os_h + t + (out_offsets ? out_offsets[b] : out_offset)
  *                and row r occupies nib[64 r .. ], qjl[8 r ..], norms[r]
- *   out_offsets  device int64[B] or NULL                                               */
+ *   out_offsets  device int64[B] or NULL
+ * qjl and norms may both be NULL: only the nibble rows are written then and the projections are
+ * skipped (V rows, whose sign bits and norms attention never reads: kernels/fused_attention.py:455-464). */
 int32_t omni_quantize_heads(const void* x, int32_t dtype, int32_t rotate,
                             const float* codebooks, int32_t cb_per_head,
                             const int32_t* user_ids, int32_t user_id,
@@ -126,7 +129,11 @@ int32_t omni_lloyd_max_fit(const float* sorted, int64_t n_total, const int64_t* 
 
 /* Row-seeded codec (kernels/quantize.py:456-499 `quantize_rows`, :502-537
  * `dequantize_rows`): row i of n_rows contiguous fp32 rows uses seed
- * (user_id mod 1024) xor (base_head_idx + i).  One shared [16] codebook. */
+ * (user_id mod 1024) xor (base_head_idx + i), for any non-negative row key base_head_idx + i below 2^31 (the
+ * reference seeds one MT19937 stream per row, kernels/quantize.py:486-492, :524-535).  Seeds below 1,024 come from
+ * the resident tables; the G of larger seeds is generated on the host and uploaded one aligned block of 1,024
+ * seeds at a time into a second, library-owned pair of tables, which makes such calls synchronise the device
+ * (about 25 us of host time per new seed).  One shared [16] codebook. */
 int32_t omni_quantize_rows(const float* x, const float* codebook, int32_t base_head_idx, int32_t user_id,
                            int64_t n_rows, uint8_t* nib, uint8_t* qjl, float* norms, void* stream);
 int32_t omni_dequantize_rows(const uint8_t* nib, const uint8_t* qjl, const float* norms,
@@ -149,7 +156,14 @@ int32_t omni_dequantize_rows(const uint8_t* nib, const uint8_t* qjl, const float
  *                hold omni_qattn_workspace_bytes(...) bytes of device scratch
  *   out          device fp32 [B][Hq][T][128]
  *   status_word  device int32 or NULL; set non-zero by the kernel if a bounded wait
- *                expires (the kernels never trap)                                        */
+ *                expires (OMNI_STATUS_WAIT_EXPIRED; the kernels never trap; the warp that
+ *                gave up leaves neutral results -- zero rows, or partial states that a
+ *                split-K merge ignores -- for the work it abandons) or if a centroid is
+ *                infinite or NaN (OMNI_STATUS_BAD_CODEBOOK)
+ * Codebooks may hold any finite fp32 centroids (kernels/quantize.py:620-636).  The tensor-core
+ * kernel dequantises through fp16 tables, which meet the 3e-3 output budget only while every
+ * |centroid| < 8; both kernels test that on the device, and a call with a wider codebook is
+ * served by the fp32 CUDA-core kernel (slower, same results as the reference's fp32 path).  */
 size_t  omni_qattn_workspace_bytes(int64_t B, int32_t Hq, int32_t T, int32_t n_splits);
 int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
                           const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
@@ -214,9 +228,14 @@ int32_t omni_qattn_decode_lora(const void* q, int32_t q_dtype,
  *     B*Hq*T*n_splits <= 63,542 partial states; larger requests return
  *     OMNI_ERR_UNSUPPORTED with a message (n_splits == 1 needs no scratch and is never
  *     rejected for size); every device that loads the library carries the 33 MiB until exit;
- *   - the FIRST call on each device resolves the arrays' device addresses and uploads the
- *     1 MiB row table with a blocking copy: make that call once, with the device current,
- *     before any stream capture begins;
+ *   - the FIRST call on each device resolves the arrays' device addresses, uploads the
+ *     1 MiB row table with a blocking copy and then waits for the whole device
+ *     (cudaDeviceSynchronize), so that a kernel on any stream, non-blocking ones included,
+ *     finds the table complete: make that call once, with the device current, before any
+ *     stream capture begins;
+ *   - there is no status_word argument: the kernels report an expired bounded wait (and a
+ *     non-finite centroid) in a status word that is also part of the library image;
+ *     omni_qattn_noalloc_status() reads it;
  *   - all calls on a device share the one scratch array.  Every partial state a launch reads
  *     is written by that same launch first, so stale contents of earlier calls are harmless,
  *     but two calls whose kernels overlap on the GPU (different streams) race on it: keep
@@ -232,6 +251,15 @@ int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
                                   int64_t ks_b, int64_t ks_h,
                                   float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out,
                                   int32_t n_splits, float* out, void* stream);
+/* Reads the status word of the allocation-free entry point on the current device into *value_out (0 = nothing
+ * to report, else an OMNI_STATUS_* value) and, with clear != 0, resets it.  Waits for the device first. */
+int32_t omni_qattn_noalloc_status(int32_t* value_out, int32_t clear);
+
+/* Self-test of the device-side bounded waits (no counterpart in the reference).  Launches one warp that waits,
+ * for at most `poll_limit` polls (1 .. 2^20), on an mbarrier nothing ever arrives on -- the same wait routine the
+ * decode kernel uses on its TMA ring.  The wait runs out, the warp writes OMNI_STATUS_WAIT_EXPIRED to
+ * `status_word` (device int32, required) and the kernel returns normally; nothing hangs, faults or traps. */
+int32_t omni_diag_bounded_wait(int32_t poll_limit, int32_t* status_word, void* stream);
 
 /* One decode step with HOST query / result buffers (the serving loop of
  * scripts/run_criteo_benchmark.py:481-560, where q arrives per step and the cache is
@@ -240,7 +268,7 @@ int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
  * two internal streams, and returns after everything has completed.  q_host/out_host
  * should be page-locked.  Remaining arguments as in omni_qattn_decode; with n_splits > 1 the workspace
  * must hold two slices of omni_qattn_workspace_bytes(ceil(B / n_chunks), Hq, T, n_splits) bytes (one per
- * internal stream). */
+ * internal stream).  status_word: device int32 or NULL, as in omni_qattn_decode. */
 int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, void* q_stage,
                                const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
                                const uint8_t* v_nib,
@@ -251,7 +279,8 @@ int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, void* q_stag
                                int64_t ks_b, int64_t ks_h,
                                float scale, int32_t with_qjl,
                                float* out_stage, float* out_host, int32_t n_chunks,
-                               int32_t n_splits, void* workspace, size_t workspace_bytes);
+                               int32_t n_splits, void* workspace, size_t workspace_bytes,
+                               int32_t* status_word);
 
 #ifdef __cplusplus
 }

@@ -50,7 +50,9 @@ SIGNATURES = {
                                          _vp, _vp]),
     "omni_qattn_decode_host": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
                                       _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _vp, _vp, _i32,
-                                      _i32, _vp, _sz]),
+                                      _i32, _vp, _sz, _vp]),
+    "omni_qattn_noalloc_status": (_i32, [_vp, _i32]),
+    "omni_diag_bounded_wait": (_i32, [_i32, _vp, _vp]),
 }
 
 _lock = threading.Lock()
@@ -190,4 +192,6 @@ def check_device_status(device: torch.device) -> None:
         w.zero_()
         if code == 7:
             raise IndexError("omni_b200: lora_indices refers to an adapter that does not exist")
+        if code == 8:
+            raise NotImplementedError("omni_b200: a codebook holds an infinite or NaN centroid")
         raise RuntimeError(f"omni_b200: a device-side bounded wait expired (status {code})")

@@ -1,25 +1,27 @@
 """Build the CUDA shared library in-tree with nvcc for sm_100a.
 
-    python -m omnistack_rs_b200.build [--force]
+    python -m omnistack_rs_b200.build [--force] [-v]
 
 The output is ``omnistack_rs_b200/csrc/libomni_b200.so``.  nvcc cross-compiles, so
-this works on a machine without a GPU.
+this works on a machine without a GPU.  Translation units are compiled in parallel into
+``csrc/_obj`` and only when they (or a header) changed; the link step follows.
 """
 from __future__ import annotations
 
+import concurrent.futures
 import os
 import shutil
 import subprocess
 import sys
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
+OBJ_DIR = os.path.join(CSRC, "_obj")
 LIB_PATH = os.path.join(CSRC, "libomni_b200.so")
-SOURCES = ["runtime.cu", "codec.cu", "codec_fast.cu", "qattn.cu", "qattn_mma.cu", "lora_q.cu", "lloyd_max.cu", "qjl_bool.cu"]
+SOURCES = ["runtime.cu", "codec.cu", "codec_fast.cu", "qattn.cu", "qattn_mma.cu", "qattn_umma.cu", "lora_q.cu",
+           "lloyd_max.cu", "qjl_bool.cu"]
 HEADERS = ["common.cuh", "qattn.cuh", "codec_fast.cuh", os.path.join("..", "..", "include", "omni_b200.h")]
-NVCC_FLAGS = [
-    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared", "-cudart", "static",
-]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
+LINK_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-cudart", "static", "-Xcompiler", "-fPIC"]
 
 
 def _nvcc() -> str:
@@ -29,25 +31,51 @@ def _nvcc() -> str:
     return exe
 
 
+def _sources():
+    return [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+
+
+def _newest_header() -> float:
+    return max(os.path.getmtime(os.path.join(CSRC, h)) for h in HEADERS)
+
+
 def is_stale() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
+    deps = [os.path.join(CSRC, s) for s in _sources() + HEADERS]
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every .cu of the library into one shared object; returns its path."""
-    if not force and not is_stale():
-        return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
-          [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB_PATH + ".tmp"]
+def _compile(src: str, verbose: bool) -> str:
+    obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
+    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        print(res.stderr)
+        raise RuntimeError(f"nvcc failed on {src}:\n" + res.stdout + res.stderr)
+    return res.stderr
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every .cu of the library and link one shared object; returns its path."""
+    if not force and not is_stale():
+        return LIB_PATH
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    hdr = _newest_header()
+    todo = []
+    for s in _sources():
+        obj = os.path.join(OBJ_DIR, os.path.splitext(s)[0] + ".o")
+        src_m = max(os.path.getmtime(os.path.join(CSRC, s)), hdr)
+        if force or verbose or not os.path.exists(obj) or os.path.getmtime(obj) < src_m:
+            todo.append(s)
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, max(1, len(todo)))) as pool:
+        for s, log in zip(todo, pool.map(lambda s: _compile(s, verbose), todo)):
+            if verbose:
+                print(f"---- {s}\n{log}")
+    objs = [os.path.join(OBJ_DIR, os.path.splitext(s)[0] + ".o") for s in _sources()]
+    res = subprocess.run([_nvcc()] + LINK_FLAGS + objs + ["-o", LIB_PATH + ".tmp"], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("link failed:\n" + res.stdout + res.stderr)
     os.replace(LIB_PATH + ".tmp", LIB_PATH)
     return LIB_PATH
 

@@ -11,6 +11,8 @@
 #include "common.cuh"
 #include "codec_fast.cuh"
 #include <cstdlib>
+#include <algorithm>
+#include <vector>
 
 namespace omni {
 
@@ -128,7 +130,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) quantize_kernel(CodecArgs
 
         const int64_t ro = b * a.os_b + h * a.os_h + t + (a.out_offsets ? a.out_offsets[b] : a.out_offset);
         reinterpret_cast<uint16_t*>(a.nib + ro * kNibBytes)[lane] = (uint16_t)packed;
-        if (lane == 0) {
+        if (lane == 0 && a.qjl) {
             *reinterpret_cast<uint2*>(a.qjl + ro * kQjlBytes) = make_uint2(lo, hi);
             a.norms[ro] = sqrtf(ss);
         }
@@ -250,10 +252,38 @@ static bool fast_kernel_allowed() {
     return !(e && e[0] == 's');
 }
 
-static int32_t quantize_common(CodecArgs& a, int32_t dtype, int32_t rotate, void* stream) {
+// Row-seeded calls: row i uses seed (user_id mod 1024) xor (base + i).  The xor only touches the low ten bits, so
+// the rows whose key base + i lies in one aligned block of 1,024 keys use exactly the seeds of that block, in a
+// permuted order.  Block 0 is the resident table; later blocks come from extended_tables_for_block.  `fn` is
+// called once per block with (first row, row count, key of the first row, tables).
+template <class Fn>
+static int32_t for_each_seed_block(int32_t base, int32_t user_id, int64_t n_rows, Fn&& fn) {
     const DeviceTables* tb = tables_for_current_device();
     if (!tb) return OMNI_ERR_NOT_INIT;
-    a.g_rows = tb->rows; a.g_cols = tb->cols;
+    for (int64_t r = 0; r < n_rows;) {
+        const int64_t key = (int64_t)base + r, block = key >> 10;
+        const int64_t end_key = std::min<int64_t>((block + 1) << 10, (int64_t)base + n_rows);
+        DeviceTables t = *tb;
+        if (block > 0) {
+            std::vector<int> slots;
+            slots.reserve((size_t)(end_key - key));
+            for (int64_t k = key; k < end_key; ++k) slots.push_back((int)(((user_id & 1023) ^ k) & 1023));
+            const int32_t rc = extended_tables_for_block(block, slots, &t);
+            if (rc != OMNI_OK) return rc;
+        }
+        const int32_t rc = fn(r, end_key - key, (int32_t)key, t);
+        if (rc != OMNI_OK) return rc;
+        r += end_key - key;
+    }
+    return OMNI_OK;
+}
+
+static int32_t quantize_common(CodecArgs& a, int32_t dtype, int32_t rotate, void* stream) {
+    if (!a.g_rows) {
+        const DeviceTables* tb = tables_for_current_device();
+        if (!tb) return OMNI_ERR_NOT_INIT;
+        a.g_rows = tb->rows; a.g_cols = tb->cols;
+    }
     cudaStream_t st = (cudaStream_t)stream;
     if (!a.row_seeded && fast_kernel_allowed()) {
         FastQuantArgs f{a.x, a.xs_b, a.xs_h, a.xs_t, a.codebooks, a.cb_per_head, a.user_ids, a.user_id, a.B, a.H, a.T,
@@ -305,7 +335,9 @@ extern "C" int32_t omni_quantize_heads(const void* x, int32_t dtype, int32_t rot
     OMNI_REQUIRE(B >= 0 && H >= 0 && T >= 0, OMNI_ERR_ARG, "omni_quantize_heads: negative extent");
     if (B == 0 || H == 0 || T == 0) return OMNI_OK;
     OMNI_REQUIRE(H <= kSeeds, OMNI_ERR_UNSUPPORTED, "omni_quantize_heads: H=%d exceeds %d heads", H, kSeeds);
-    OMNI_REQUIRE(x && codebooks && nib && qjl && norms, OMNI_ERR_ARG, "omni_quantize_heads: NULL buffer");
+    OMNI_REQUIRE(x && codebooks && nib, OMNI_ERR_ARG, "omni_quantize_heads: NULL buffer");
+    OMNI_REQUIRE((qjl == nullptr) == (norms == nullptr), OMNI_ERR_ARG,
+                 "omni_quantize_heads: qjl and norms must both be given or both be NULL (nibble rows only)");
     const size_t in_align = dtype == OMNI_F32 ? 16 : 8;
     OMNI_REQUIRE(aligned(x, in_align) && xs_b % 4 == 0 && xs_h % 4 == 0 && xs_t % 4 == 0, OMNI_ERR_ARG,
                  "omni_quantize_heads: input rows must be %zu-byte aligned (strides multiples of 4 elements)", in_align);
@@ -325,24 +357,29 @@ extern "C" int32_t omni_quantize_rows(const float* x, const float* codebook, int
                                       int64_t n_rows, uint8_t* nib, uint8_t* qjl, float* norms, void* stream) {
     OMNI_REQUIRE(n_rows >= 0, OMNI_ERR_ARG, "omni_quantize_rows: n_rows < 0");
     if (n_rows == 0) return OMNI_OK;
-    OMNI_REQUIRE(base_head_idx >= 0 && base_head_idx + n_rows <= kSeeds, OMNI_ERR_UNSUPPORTED,
-                 "omni_quantize_rows: row keys [%d, %lld) leave the %d-seed table", base_head_idx,
-                 (long long)(base_head_idx + n_rows), kSeeds);
+    OMNI_REQUIRE(base_head_idx >= 0 && (int64_t)base_head_idx + n_rows <= 0x7fffffffLL, OMNI_ERR_UNSUPPORTED,
+                 "omni_quantize_rows: row keys [%d, %lld) leave the 31-bit key space", base_head_idx,
+                 (long long)(base_head_idx + n_rows));
     OMNI_REQUIRE(x && codebook && nib && qjl && norms, OMNI_ERR_ARG, "omni_quantize_rows: NULL buffer");
     OMNI_REQUIRE(aligned(x, 16) && aligned(qjl, 8) && aligned(nib, 2), OMNI_ERR_ARG, "omni_quantize_rows: misaligned buffer");
-    CodecArgs a{};
-    a.x = x; a.xs_b = kHeadDim; a.xs_h = 0; a.xs_t = 0;
-    a.codebooks = codebook; a.cb_per_head = 0; a.user_id = user_id;
-    a.B = n_rows; a.H = 1; a.T = 1;
-    a.nib = nib; a.qjl = qjl; a.norms = norms; a.os_b = 1; a.os_h = 0;
-    a.row_seeded = 1; a.base_head_idx = base_head_idx;
-    return quantize_common(a, OMNI_F32, 0, stream);
+    return for_each_seed_block(base_head_idx, user_id, n_rows, [&](int64_t r0, int64_t n, int32_t key0, const DeviceTables& t) {
+        CodecArgs a{};
+        a.x = x + r0 * kHeadDim; a.xs_b = kHeadDim; a.xs_h = 0; a.xs_t = 0;
+        a.codebooks = codebook; a.cb_per_head = 0; a.user_id = user_id;
+        a.B = n; a.H = 1; a.T = 1;
+        a.nib = nib + r0 * kNibBytes; a.qjl = qjl + r0 * kQjlBytes; a.norms = norms + r0; a.os_b = 1; a.os_h = 0;
+        a.row_seeded = 1; a.base_head_idx = key0;
+        a.g_rows = t.rows; a.g_cols = t.cols;
+        return quantize_common(a, OMNI_F32, 0, stream);
+    });
 }
 
 static int32_t dequantize_common(CodecArgs& a, void* stream) {
-    const DeviceTables* tb = tables_for_current_device();
-    if (!tb) return OMNI_ERR_NOT_INIT;
-    a.g_rows = tb->rows; a.g_cols = tb->cols;
+    if (!a.g_rows) {
+        const DeviceTables* tb = tables_for_current_device();
+        if (!tb) return OMNI_ERR_NOT_INIT;
+        a.g_rows = tb->rows; a.g_cols = tb->cols;
+    }
     if (!a.row_seeded) {
         const int grid = grid_for_rows(a.B * a.H * ((a.T + kDeqRun - 1) / kDeqRun));
         dequantize_heads_kernel<<<grid, kWarpsPerBlock * 32, 0, (cudaStream_t)stream>>>(a);
@@ -377,17 +414,22 @@ extern "C" int32_t omni_dequantize_rows(const uint8_t* nib, const uint8_t* qjl, 
                                         int64_t n_rows, int32_t with_qjl, float* out, void* stream) {
     OMNI_REQUIRE(n_rows >= 0, OMNI_ERR_ARG, "omni_dequantize_rows: n_rows < 0");
     if (n_rows == 0) return OMNI_OK;
-    OMNI_REQUIRE(base_head_idx >= 0 && base_head_idx + n_rows <= kSeeds, OMNI_ERR_UNSUPPORTED,
-                 "omni_dequantize_rows: row keys [%d, %lld) leave the %d-seed table", base_head_idx,
-                 (long long)(base_head_idx + n_rows), kSeeds);
+    OMNI_REQUIRE(base_head_idx >= 0 && (int64_t)base_head_idx + n_rows <= 0x7fffffffLL, OMNI_ERR_UNSUPPORTED,
+                 "omni_dequantize_rows: row keys [%d, %lld) leave the 31-bit key space", base_head_idx,
+                 (long long)(base_head_idx + n_rows));
     OMNI_REQUIRE(nib && codebook && out && (!with_qjl || (qjl && norms)), OMNI_ERR_ARG, "omni_dequantize_rows: NULL buffer");
     OMNI_REQUIRE(aligned(out, 16) && aligned(nib, 2) && (!with_qjl || aligned(qjl, 8)), OMNI_ERR_ARG,
                  "omni_dequantize_rows: misaligned buffer");
-    CodecArgs a{};
-    a.codebooks = codebook; a.cb_per_head = 0; a.user_id = user_id;
-    a.B = n_rows; a.H = 1; a.T = 1;
-    a.nib = const_cast<uint8_t*>(nib); a.qjl = const_cast<uint8_t*>(qjl); a.norms = const_cast<float*>(norms);
-    a.os_b = 1; a.os_h = 0; a.with_qjl = with_qjl; a.out = out;
-    a.row_seeded = 1; a.base_head_idx = base_head_idx;
-    return dequantize_common(a, stream);
+    return for_each_seed_block(base_head_idx, user_id, n_rows, [&](int64_t r0, int64_t n, int32_t key0, const DeviceTables& t) {
+        CodecArgs a{};
+        a.codebooks = codebook; a.cb_per_head = 0; a.user_id = user_id;
+        a.B = n; a.H = 1; a.T = 1;
+        a.nib = const_cast<uint8_t*>(nib) + r0 * kNibBytes;
+        a.qjl = qjl ? const_cast<uint8_t*>(qjl) + r0 * kQjlBytes : nullptr;
+        a.norms = norms ? const_cast<float*>(norms) + r0 : nullptr;
+        a.os_b = 1; a.os_h = 0; a.with_qjl = with_qjl; a.out = out + r0 * kHeadDim;
+        a.row_seeded = 1; a.base_head_idx = key0;
+        a.g_rows = t.rows; a.g_cols = t.cols;
+        return dequantize_common(a, stream);
+    });
 }

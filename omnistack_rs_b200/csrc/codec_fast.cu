@@ -310,7 +310,9 @@ __device__ __forceinline__ void stage_row(uint32_t buf, const void* x, int64_t i
     for (int k = 0; k < Row32<DT>::kChunks; ++k) cp_async16(buf + k * 512, src + 16 * k);
 }
 
-template <int DT, bool ROTATE>
+// SIGNS = false: only the nibble rows are produced (a.qjl and a.norms are null): V rows of a cache whose attention
+// never reads their sign bits or norms skip the projections altogether.
+template <int DT, bool ROTATE, bool SIGNS>
 __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQuantArgs a) {
     extern __shared__ __align__(16) unsigned char fq_smem[];
     const int n_tabs = a.cb_per_head ? a.H : 1;
@@ -334,7 +336,7 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
         const uint32_t* grow = a.g_rows + (size_t)seed * kQjlDim * 4;
         // A fragments of G for this lane: m-tile mt (16 projections), k-step ks (8 of this lane's dims)
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
+        for (int mt = 0; SIGNS && mt < 4; ++mt) {
             const uint32_t w0 = __ldg(grow + (16 * mt + g) * 4 + t), w1 = __ldg(grow + (16 * mt + g + 8) * 4 + t);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
@@ -399,6 +401,11 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
                     codes[i >> 3] |= (uint32_t)c << (4 * (i & 7));
                     y[i] = __fsub_rn(y[i], ht.cb[c]);
                 }
+            }
+            if (!SIGNS) {
+                if (active)
+                    *reinterpret_cast<uint4*>(a.nib + (out_base + tr) * kNibBytes + 16 * t) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+                continue;
             }
             // ---- residual norm and fixed-point scale ------------------------------------------------
             float ss = 0.f, emax = 0.f;
@@ -560,6 +567,7 @@ bool fast_quantize_eligible(const FastQuantArgs& a, int dtype) {
     if (a.cb_per_head && a.H > kFqMaxHeads) return false;
     if (!fq_aligned(a.x, 16) || a.xs_b % vec || a.xs_h % vec || a.xs_t % vec) return false;
     if (!fq_aligned(a.nib, 16) || !fq_aligned(a.qjl, 2)) return false;
+    if ((a.qjl == nullptr) != (a.norms == nullptr)) return false;
     return a.T > 0;
 }
 
@@ -574,7 +582,9 @@ static int32_t launch_fast_t(const FastQuantArgs& a, int rotate, cudaStream_t st
     const int64_t pairs = a.B * a.H;
     int64_t blocks = (pairs + kFqWarps - 1) / kFqWarps;
     if (blocks > 2 * sms) blocks = 2 * sms;
-    auto kern = rotate ? fast_quantize_kernel<DT, true> : fast_quantize_kernel<DT, false>;
+    const bool signs = a.qjl != nullptr;
+    auto kern = signs ? (rotate ? fast_quantize_kernel<DT, true, true> : fast_quantize_kernel<DT, false, true>)
+                      : (rotate ? fast_quantize_kernel<DT, true, false> : fast_quantize_kernel<DT, false, false>);
     {   // opt in once per (kernel, device) to the shared memory of the largest table count the kernel accepts
         static std::mutex mu;
         static std::vector<std::pair<const void*, int>> done;

@@ -6,6 +6,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <vector>
 #include "../../include/omni_b200.h"
 
 namespace omni {
@@ -33,6 +34,10 @@ struct DeviceTables {
 
 const DeviceTables* tables_for_current_device();   // nullptr (and error set) if not initialised
 const uint32_t* host_rows_table();                 // host copy, built on first use
+// Tables of the aligned seed block [1024 * block, 1024 * block + 1024), block >= 1, with at least the seeds
+// 1024 * block + j for j in `slots` filled in (generated on the host and uploaded on demand; one block is resident
+// per device at a time, and switching blocks synchronises the device).
+int32_t extended_tables_for_block(int64_t block, const std::vector<int>& slots, DeviceTables* out);
 
 int32_t set_error(int32_t code, const char* fmt, ...);
 int32_t check_cuda(cudaError_t e, const char* what);

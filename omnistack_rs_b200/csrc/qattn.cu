@@ -27,9 +27,16 @@ __global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(Att
     __shared__ float cb_s[kAttnWarps][16];
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
-    const int64_t work = (int64_t)blockIdx.x * kAttnWarps + wib;
+    if (a.only_if_wide) {
+        // launched behind the tensor-core kernel: that kernel served the call unless some centroid is outside the
+        // range of its fp16 table (same test there), in which case it stood down and this one does the work in fp32
+        const int n_cb = a.cb_per_head ? a.Hkv * 16 : 16;
+        bool wide = false;
+        for (int i = threadIdx.x; i < n_cb; i += blockDim.x) wide = wide || centroid_is_wide(__ldg(a.codebooks + i));
+        if (!__syncthreads_or(wide)) return;
+    }
     const int64_t n_work = a.B * a.Hq * a.T * a.n_splits;
-    if (work >= n_work) return;
+    for (int64_t work = (int64_t)blockIdx.x * kAttnWarps + wib; work < n_work; work += (int64_t)gridDim.x * kAttnWarps) {
     const int split = (int)(work % a.n_splits);
     int64_t rest = work / a.n_splits;
     const int64_t qrow = rest;                       // index into q / out: ((b*Hq + hq)*T + tq)
@@ -43,7 +50,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(Att
     Elem<DT>::load4(a.q, qrow * kHeadDim + 4 * lane, qv);
     if (a.rotate_q) wht128_warp(qv, lane);
     *reinterpret_cast<float4*>(&q_s[wib][4 * lane]) = make_float4(qv[0], qv[1], qv[2], qv[3]);
-    if (lane < 16) cb_s[wib][lane] = __ldg(a.codebooks + (a.cb_per_head ? hkv * 16 : 0) + lane);
+    {
+        const float c = __ldg(a.codebooks + (a.cb_per_head ? hkv * 16 : 0) + (lane & 15));
+        if (lane < 16) cb_s[wib][lane] = c;
+        // an infinite or NaN centroid has no meaningful attention result: say so through the status word
+        if (__any_sync(kFullMask, !isfinite(c)) && lane == 0 && a.status) atomicExch(a.status, OMNI_STATUS_BAD_CODEBOOK);
+    }
     __syncwarp();
     if (a.with_qjl) {
         const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
@@ -174,6 +186,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(Att
         *reinterpret_cast<float4*>(w + 4 * lane) = make_float4(O[0], O[1], O[2], O[3]);
         if (lane == 0) { w[128] = m_w; w[129] = l_w; }
     }
+    __syncwarp();                      // the next unit overwrites this warp's query row in shared memory
+    }
 }
 
 // Merge the per-split partial states of one (user, head, token).  A CTA per output row; its warps take the splits
@@ -278,14 +292,21 @@ static int32_t launch(const AttnArgs& a, cudaStream_t st) {
             m.work_counter = reinterpret_cast<uint32_t*>(a.ws + (size_t)a.B * a.Hq * a.T * a.n_splits * kWsStride);
         const int32_t rc = launch_mma(m, st);
         if (rc != OMNI_OK) return rc;
-    } else {
+    }
+    {
+        // The lane-per-key kernel: the call's only kernel for small shapes; behind the tensor-core kernel it is a
+        // stand-by that returns at once unless the codebooks are outside the fp16 table's range (decided on the
+        // device by both kernels with the same test), so a persistent-size grid suffices there.
+        AttnArgs l = a;
+        l.only_if_wide = use_mma ? 1 : 0;
         const int64_t n_work = a.B * a.Hq * a.T * a.n_splits;
-        const int64_t blocks = (n_work + kAttnWarps - 1) / kAttnWarps;
-        OMNI_REQUIRE(blocks <= 0x7fffffffLL, OMNI_ERR_UNSUPPORTED, "qattn: %lld work units exceed one grid", (long long)n_work);
+        int64_t blocks = (n_work + kAttnWarps - 1) / kAttnWarps;
+        const int64_t cap = use_mma ? 148 * 8 : 148 * 64;
+        if (blocks > cap) blocks = cap;
         switch (a.q_dtype) {
-            case OMNI_F32:  qattn_lane_per_key_kernel<OMNI_F32><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(a); break;
-            case OMNI_BF16: qattn_lane_per_key_kernel<OMNI_BF16><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(a); break;
-            case OMNI_F16:  qattn_lane_per_key_kernel<OMNI_F16><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(a); break;
+            case OMNI_F32:  qattn_lane_per_key_kernel<OMNI_F32><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(l); break;
+            case OMNI_BF16: qattn_lane_per_key_kernel<OMNI_BF16><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(l); break;
+            case OMNI_F16:  qattn_lane_per_key_kernel<OMNI_F16><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(l); break;
             default: return set_error(OMNI_ERR_ARG, "qattn: unknown q dtype code %d", a.q_dtype);
         }
         OMNI_CUDA(cudaGetLastError());
@@ -314,8 +335,9 @@ constexpr size_t kStaticScratchBytes = 32u << 20;                       // 32 Mi
 constexpr size_t kStaticRowsWords = (size_t)kSeeds * kQjlDim * 4;        // 1 MiB of G rows
 static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
 static __device__ __align__(256) uint32_t g_static_rows[kStaticRowsWords];
+static __device__ __align__(256) int32_t g_static_status[64];                   // word 0: the entry point's status word
 
-struct StaticArrays { float* scratch = nullptr; uint32_t* rows = nullptr; };
+struct StaticArrays { float* scratch = nullptr; uint32_t* rows = nullptr; int32_t* status = nullptr; };
 static StaticArrays g_static[kMaxDevices];
 static std::mutex g_static_mutex;
 
@@ -329,9 +351,16 @@ static int32_t static_arrays_for_current_device(StaticArrays* out) {
         float* scratch = nullptr;
         uint32_t* rows = nullptr;
         OMNI_CUDA(cudaGetSymbolAddress((void**)&scratch, g_static_scratch));
+        int32_t* status = nullptr;
         OMNI_CUDA(cudaGetSymbolAddress((void**)&rows, g_static_rows));
+        OMNI_CUDA(cudaGetSymbolAddress((void**)&status, g_static_status));
         OMNI_CUDA(cudaMemcpy(rows, host_rows_table(), kStaticRowsWords * sizeof(uint32_t), cudaMemcpyHostToDevice));
+        // The copy above comes from pageable host memory on the legacy stream: it may return once the data is staged,
+        // and a non-blocking stream of the caller has no ordering with the legacy stream at all.  Wait for the device
+        // before the table is published, so the first kernel on any stream reads complete rows.
+        OMNI_CUDA(cudaDeviceSynchronize());
         g_static[dev].rows = rows;
+        g_static[dev].status = status;
         g_static[dev].scratch = scratch;
     }
     *out = g_static[dev];
@@ -417,7 +446,8 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
                                           int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                                           int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
                                           float* out_stage, float* out_host, int32_t n_chunks,
-                                          int32_t n_splits, void* workspace, size_t workspace_bytes) {
+                                          int32_t n_splits, void* workspace, size_t workspace_bytes,
+                                          int32_t* status_word) {
     const DeviceTables* tb = tables_for_current_device();
     if (!tb) return OMNI_ERR_NOT_INIT;
     OMNI_REQUIRE(q_host && q_stage && out_stage && out_host, OMNI_ERR_ARG, "qattn_decode_host: NULL buffer");
@@ -456,7 +486,7 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
                    seq_lens ? seq_lens + b0 : nullptr, cache_slots ? cache_slots + b0 : nullptr,
                    nb, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, 0, 0, n_splits,
                    n_splits > 1 ? reinterpret_cast<float*>((char*)workspace + (size_t)(c & 1) * ws_chunk) : nullptr,
-                   out_stage + qoff, tb->rows, nullptr};
+                   out_stage + qoff, tb->rows, status_word};
         int32_t stc = validate(a, ws_chunk);
         if (stc == OMNI_OK) stc = launch(a, st);
         if (stc != OMNI_OK) { cudaStreamSynchronize(g_hs[dev].s[0]); cudaStreamSynchronize(g_hs[dev].s[1]); return stc; }
@@ -489,8 +519,26 @@ extern "C" int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
     if (st != OMNI_OK) return st;
     AttnArgs a{q, q_dtype, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id, seq_lens,
                cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
-               arr.scratch, out, arr.rows, nullptr};
+               arr.scratch, out, arr.rows, arr.status};
     st = validate(a, kStaticScratchBytes);
     if (st != OMNI_OK) return st;
     return launch(a, (cudaStream_t)stream);
+}
+
+extern "C" int32_t omni_qattn_noalloc_status(int32_t* value_out, int32_t clear) {
+    OMNI_REQUIRE(value_out != nullptr, OMNI_ERR_ARG, "omni_qattn_noalloc_status: value_out is NULL");
+    StaticArrays arr;
+    int32_t st = static_arrays_for_current_device(&arr);
+    if (st != OMNI_OK) return st;
+    OMNI_CUDA(cudaDeviceSynchronize());
+    OMNI_CUDA(cudaMemcpy(value_out, arr.status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    if (clear && *value_out != 0) OMNI_CUDA(cudaMemset(arr.status, 0, sizeof(int32_t)));
+    return OMNI_OK;
+}
+
+extern "C" int32_t omni_diag_bounded_wait(int32_t poll_limit, int32_t* status_word, void* stream) {
+    OMNI_REQUIRE(poll_limit >= 1 && poll_limit <= (1 << 20), OMNI_ERR_ARG,
+                 "omni_diag_bounded_wait: poll_limit %d outside [1, 2^20]", poll_limit);
+    OMNI_REQUIRE(status_word != nullptr, OMNI_ERR_ARG, "omni_diag_bounded_wait: status_word is NULL");
+    return launch_wait_probe((uint32_t)poll_limit, status_word, (cudaStream_t)stream);
 }

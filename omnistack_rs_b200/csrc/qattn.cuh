@@ -16,7 +16,18 @@ struct AttnArgs {
     int32_t* status;           // device word set non-zero when a bounded wait expires (may be null)
     uint32_t* work_counter;    // kWorkCounterBytes of device memory behind the split-K partials: one ticket counter
                                // per kv head for the tensor-core kernel (null: items are assigned statically)
+    int only_if_wide;          // lane-per-key kernel: 1 = run only when the codebooks are outside the fp16 table's
+                               // range (it then completes a call whose tensor-core launch stood down), 0 = always
 };
+
+// The tensor-core kernel dequantises through a table of fp16 centroid pairs.  fp16 rounds a centroid by at most
+// 2^-9 = 1.95e-3 while |c| < 8 (1e-3 below 4, where Lloyd-Max codebooks of rotated unit-variance data lie) and by
+// up to 3.9e-3 from 8 on, which a 3e-3 output budget cannot absorb; codebooks with a centroid of magnitude 8 or
+// more, infinite or NaN ("wide") are served by the fp32 lane-per-key kernel instead.  Both kernels evaluate this
+// same predicate on the device (over every codebook of the call), so the choice needs no host copy and cannot go
+// stale.
+constexpr float kFp16CentroidLimit = 8.0f;
+__device__ __forceinline__ bool centroid_is_wide(float c) { return !(fabsf(c) < kFp16CentroidLimit); }
 
 constexpr int kWsStride = 132;     // floats per split-K partial: 128 accumulators, max, sum, 2 pad
 constexpr size_t kWorkCounterBytes = 4096;   // kSeeds (the most kv heads a call may have) 32-bit counters
@@ -35,5 +46,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Tensor-core kernel (qattn_mma.cu): shapes it covers, and its launcher.
 bool mma_eligible(const AttnArgs& a);
 int32_t launch_mma(const AttnArgs& a, cudaStream_t st);
+// One-warp kernel that lets a bounded mbarrier wait run out on purpose (nothing arrives on its barrier).
+int32_t launch_wait_probe(uint32_t limit, int32_t* status, cudaStream_t st);
 
 }  // namespace omni

@@ -184,9 +184,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// bounded wait: false when kWaitLimit attempts did not see the phase complete
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i)
+// bounded wait: false when `limit` attempts did not see the phase complete
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = kWaitLimit) {
+    for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
@@ -403,6 +403,14 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
     const uint32_t my_off = (uint32_t)warp < n_front ? (uint32_t)warp * kWarpBlockBytes
                                                      : lut_off + kLutSpan + ((uint32_t)warp - n_front) * kWarpBlockBytes;
     {
+        // a codebook the fp16 table cannot hold to the error budget: the whole grid stands down (the same test in
+        // the lane-per-key kernel, launched behind this one, makes that kernel serve the call)
+        const int n_cb = a.cb_per_head ? a.Hkv * 16 : 16;
+        bool wide = false;
+        for (int i = threadIdx.x; i < n_cb; i += blockDim.x) wide = wide || centroid_is_wide(__ldg(a.codebooks + i));
+        if (__syncthreads_or(wide)) return;
+    }
+    {
         const float* cb = a.codebooks + (a.cb_per_head ? cb_head * 16 : 0);
         uint32_t* lut = reinterpret_cast<uint32_t*>(smem + lut_off);
         for (int i = threadIdx.x; i < 256 * 8; i += blockDim.x) {       // four lanes' copies of an entry per store
@@ -445,7 +453,7 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
     // starts the current one, so the atomic's latency is covered by the item's own work.
     const int64_t item_stride = (int64_t)gridDim.x * kMmaWarps;
     uint32_t* const counter = a.work_counter ? a.work_counter + blockIdx.y : nullptr;
-    for (int64_t item = (int64_t)warp * gridDim.x + blockIdx.x; alive && item < n_items;) {
+    for (int64_t item = (int64_t)warp * gridDim.x + blockIdx.x; item < n_items;) {
         uint32_t ticket = 0u;
         if (counter && lane == 0) ticket = atomicAdd(counter, 1u);
         int64_t rest = item;
@@ -468,7 +476,8 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         const int64_t s1 = (s0 + per < len) ? s0 + per : len;
         const int64_t slot = a.cache_slots ? (int64_t)a.cache_slots[b] : b;
         const int64_t row0 = slot * a.ks_b + (int64_t)hkv * a.ks_h + s0;
-        const int nkeys = s1 > s0 ? (int)(s1 - s0) : 0;
+        // a warp whose wait expired earlier reads nothing more: its remaining items get neutral results below
+        const int nkeys = (alive && s1 > s0) ? (int)(s1 - s0) : 0;
         // full stages come in by TMA, whose row coordinate is a signed 32-bit number; the rest (fewer than 32 keys,
         // or every key of a range that lies beyond that coordinate space) is read with plain loads
         const int nstage = (row0 + nkeys <= 0x7fffffffLL) ? nkeys / kStageKeys : 0;
@@ -624,7 +633,8 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         // ---- full stages: wait, pull the bytes of a 16-key block into registers, process; refill -----
         KeyBlock kb;
         for (int j = 0; j < nstage; ++j) {
-            if (!mbar_wait_bounded(ring.bar0 + 8 * ring.use, ring.use_phase)) { alive = false; break; }
+            // the outcome is made warp-uniform: the lanes poll on their own and could disagree at the limit
+            if (!__all_sync(kFullMask, mbar_wait_bounded(ring.bar0 + 8 * ring.use, ring.use_phase))) { alive = false; break; }
             const uint32_t base = ring.stage0 + ring.use * kStageBytes;
             // both 16-key blocks of the stage are pulled into registers up front, so that the table lookups of the
             // second block can overlap the softmax of the first
@@ -657,8 +667,23 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
             __syncwarp();
             if (j + kStages < nstage) ring_issue(ring, &map_k, &map_v, (int32_t)(row0 + kStageKeys * (j + kStages)), lane);
         }
-        if (!alive) break;
-        for (int k0 = nstage * kStageKeys; k0 < nkeys; k0 += 16) {     // blocks with plain clamped loads
+        if (!alive && ring.in_flight) {
+            // A wait expired.  Report it, give the copies still in flight a bounded chance to land before this
+            // warp's shared memory is handed back, and turn the item's state into the neutral partial result
+            // (maximum -inf, sum 0, zero accumulators) so that a merge never reads memory this launch left unwritten.
+            if (lane == 0 && a.status) atomicExch(a.status, OMNI_ERR_DEVICE_WAIT);
+            while (ring.in_flight) {
+                mbar_wait_bounded(ring.bar0 + 8 * ring.use, ring.use_phase);
+                ring_consumed(ring);
+            }
+            __syncwarp();
+        }
+        if (!alive) {
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) { st.O[mt][0] = 0.f; st.O[mt][1] = 0.f; st.O[mt][2] = 0.f; st.O[mt][3] = 0.f; }
+            st.m0 = -INFINITY; st.m1 = -INFINITY; st.l0 = 0.f; st.l1 = 0.f;
+        }
+        for (int k0 = nstage * kStageKeys; alive && k0 < nkeys; k0 += 16) {     // blocks with plain clamped loads
             const int nvalid = nkeys - k0 < 16 ? nkeys - k0 : 16;
             load_tail_block<QJL>(kb, a, row0 + k0, nvalid, kr, va, vb, g, t);
             process_key_block<QJL, true, ONECOL>(kb, st, qB, sg, post0, post1, lut_lane, nvalid, kr);
@@ -729,16 +754,6 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         }
         item = counter ? item_stride + (int64_t)__shfl_sync(kFullMask, ticket, 0) : item + item_stride;
     }
-
-    if (!alive) {
-        // A wait expired.  Report it, then give the copies still in flight a bounded chance to land
-        // before this warp's shared memory is handed back.
-        if (lane == 0 && a.status) atomicExch(a.status, OMNI_ERR_DEVICE_WAIT);
-        while (ring.in_flight) {
-            mbar_wait_bounded(ring.bar0 + 8 * ring.use, ring.use_phase);
-            ring_consumed(ring);
-        }
-    }
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -799,6 +814,26 @@ static int32_t encode_nibble_map(CUtensorMap* map, const uint8_t* base) {
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     OMNI_REQUIRE(r == CUDA_SUCCESS, OMNI_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return OMNI_OK;
+}
+
+// Self-test of the bounded wait: one warp waits, with the caller's poll limit, on an mbarrier that nothing ever
+// arrives on.  The wait must run out, the warp must report OMNI_ERR_DEVICE_WAIT through the status word exactly
+// like the decode kernel does, and the kernel must return normally (nothing spins unbounded, nothing traps).
+__global__ void bounded_wait_probe_kernel(uint32_t limit, int32_t* status) {
+    __shared__ __align__(8) unsigned long long bar_storage;
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&bar_storage);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncwarp();
+    const bool ok = __all_sync(kFullMask, mbar_wait_bounded(bar, 0u, limit));
+    if (!ok && threadIdx.x == 0 && status) atomicExch(status, OMNI_ERR_DEVICE_WAIT);
+}
+
+int32_t launch_wait_probe(uint32_t limit, int32_t* status, cudaStream_t st) {
+    bounded_wait_probe_kernel<<<1, 32, 0, st>>>(limit, status);
+    return check_cuda(cudaGetLastError(), "bounded_wait_probe_kernel launch");
 }
 
 bool mma_eligible(const AttnArgs& a) {

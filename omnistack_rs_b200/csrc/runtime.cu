@@ -4,6 +4,7 @@
 #include <string>
 #include <vector>
 #include <cstring>
+#include <algorithm>
 
 namespace omni {
 
@@ -58,23 +59,77 @@ struct Mt19937 {
     }
 };
 
+// G of one seed in both layouts: rows[64][4] (bit d of projection i -> word d/32, bit d%32) and
+// cols[128] (bit i of entry d); both must be zero on entry.
+void fill_seed(uint32_t seed, uint32_t* rows, uint64_t* cols) {
+    Mt19937 gen(seed);
+    for (int i = 0; i < kQjlDim; ++i)
+        for (int d = 0; d < kHeadDim; ++d) {
+            uint32_t bit = gen.next() & 1u;
+            rows[i * 4 + (d >> 5)] |= bit << (d & 31);
+            cols[d] |= (uint64_t)bit << i;
+        }
+}
+
 void build_host_tables_locked() {
     if (!g_host_rows.empty()) return;
     g_host_rows.assign((size_t)kSeeds * kQjlDim * 4, 0u);
     g_host_cols.assign((size_t)kSeeds * kHeadDim, 0ull);
-    for (int seed = 0; seed < kSeeds; ++seed) {
-        Mt19937 gen((uint32_t)seed);
-        uint32_t* rows = &g_host_rows[(size_t)seed * kQjlDim * 4];
-        uint64_t* cols = &g_host_cols[(size_t)seed * kHeadDim];
-        for (int i = 0; i < kQjlDim; ++i)
-            for (int d = 0; d < kHeadDim; ++d) {
-                uint32_t bit = gen.next() & 1u;
-                rows[i * 4 + (d >> 5)] |= bit << (d & 31);
-                cols[d] |= (uint64_t)bit << i;
-            }
-    }
+    for (int seed = 0; seed < kSeeds; ++seed)
+        fill_seed((uint32_t)seed, &g_host_rows[(size_t)seed * kQjlDim * 4], &g_host_cols[(size_t)seed * kHeadDim]);
 }
+
+// Seeds at or above 1,024 (the row-seeded codec reaches them once its row key passes 1,023): one aligned block
+// of 1,024 seeds at a time lives in a second pair of device tables, filled on demand from the host generator.
+struct ExtBlock {
+    uint32_t* rows = nullptr;      // device [1024][64][4]
+    uint64_t* cols = nullptr;      // device [1024][128]
+    int64_t block = -1;            // seeds [1024 * block, 1024 * block + 1024) are (partly) resident
+    std::vector<uint8_t> have;     // which seeds of the block have been uploaded
+};
+ExtBlock g_ext[kMaxDevices];
 }  // namespace
+
+int32_t extended_tables_for_block(int64_t block, const std::vector<int>& slots, DeviceTables* out) {
+    int dev = -1;
+    OMNI_CUDA(cudaGetDevice(&dev));
+    OMNI_REQUIRE(dev >= 0 && dev < kMaxDevices, OMNI_ERR_ARG, "device index %d out of range", dev);
+    OMNI_REQUIRE(block >= 1 && block < (1ll << 22), OMNI_ERR_UNSUPPORTED, "row keys beyond 2^32 are not supported");
+    std::lock_guard<std::mutex> lk(g_mutex);
+    ExtBlock& e = g_ext[dev];
+    if (!e.rows) {
+        OMNI_CUDA(cudaMalloc(&e.rows, (size_t)kSeeds * kQjlDim * 4 * sizeof(uint32_t)));
+        OMNI_CUDA(cudaMalloc(&e.cols, (size_t)kSeeds * kHeadDim * sizeof(uint64_t)));
+    }
+    bool synced = false;
+    if (e.block != block) {
+        // kernels of an earlier call may still read the previous block
+        OMNI_CUDA(cudaDeviceSynchronize());
+        synced = true;
+        e.block = block;
+        e.have.assign(kSeeds, 0);
+    }
+    std::vector<uint32_t> rows((size_t)kQjlDim * 4);
+    std::vector<uint64_t> cols((size_t)kHeadDim);
+    bool uploaded = false;
+    for (int j : slots) {
+        if (j < 0 || j >= kSeeds || e.have[j]) continue;
+        if (!synced) { OMNI_CUDA(cudaDeviceSynchronize()); synced = true; }
+        std::fill(rows.begin(), rows.end(), 0u);
+        std::fill(cols.begin(), cols.end(), 0ull);
+        fill_seed((uint32_t)(block * kSeeds + j), rows.data(), cols.data());
+        OMNI_CUDA(cudaMemcpy(e.rows + (size_t)j * kQjlDim * 4, rows.data(), rows.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+        OMNI_CUDA(cudaMemcpy(e.cols + (size_t)j * kHeadDim, cols.data(), cols.size() * sizeof(uint64_t), cudaMemcpyHostToDevice));
+        e.have[j] = 1;
+        uploaded = true;
+    }
+    // copies from pageable memory may return before the data has landed, and a caller's non-blocking stream is not
+    // ordered behind them: wait for the device before a kernel may use the tables
+    if (uploaded) OMNI_CUDA(cudaDeviceSynchronize());
+    out->rows = e.rows;
+    out->cols = e.cols;
+    return OMNI_OK;
+}
 
 const uint32_t* host_rows_table() {
     std::lock_guard<std::mutex> lk(g_mutex);
@@ -100,7 +155,7 @@ const DeviceTables* tables_for_current_device() {
 
 using namespace omni;
 
-extern "C" int32_t omni_abi_version(void) { return 1; }
+extern "C" int32_t omni_abi_version(void) { return 2; }
 
 extern "C" const char* omni_last_error(void) { return g_last_error.c_str(); }
 
@@ -130,6 +185,8 @@ extern "C" int32_t omni_init(int32_t device) {
     if (e == cudaSuccess) e = cudaMalloc(&cols, g_host_cols.size() * sizeof(uint64_t));
     if (e == cudaSuccess) e = cudaMemcpy(rows, g_host_rows.data(), g_host_rows.size() * sizeof(uint32_t), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(cols, g_host_cols.data(), g_host_cols.size() * sizeof(uint64_t), cudaMemcpyHostToDevice);
+    // pageable copies may return once staged; a non-blocking stream is not ordered behind them: wait for the device
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
         if (rows) cudaFree(rows);
         if (cols) cudaFree(cols);
@@ -153,6 +210,14 @@ extern "C" int32_t omni_shutdown(void) {
             cudaFree(g_tables[d].cols);
         }
         g_tables[d] = DeviceTables();
+    }
+    for (int d = 0; d < kMaxDevices; ++d) {
+        if (!g_ext[d].rows && !g_ext[d].cols) continue;
+        if (cudaSetDevice(d) == cudaSuccess) {
+            cudaFree(g_ext[d].rows);
+            cudaFree(g_ext[d].cols);
+        }
+        g_ext[d] = ExtBlock();
     }
     cudaSetDevice(prev);
     return OMNI_OK;

@@ -88,13 +88,17 @@ def rotate_quantize_append(x_new: torch.Tensor, cache_nib: torch.Tensor, cache_q
                            *, rotate: bool = True) -> None:
     """Rotate + quantize ``x_new`` (B, H, T_new, 128) and write the packed rows into the
     caches ``(B, H, S_max, 64|8|-)`` starting at key index ``offsets[b]`` (int tensor (B,) or
-    one int).  Equals ``quantize_heads(_wht_torch(x_new))`` stored at that offset."""
+    one int).  Equals ``quantize_heads(_wht_torch(x_new))`` stored at that offset.  ``cache_qjl`` and
+    ``cache_norms`` may both be ``None``: only the nibble rows are produced then (V rows: attention reads
+    neither their sign bits nor their norms) and the projections are skipped."""
     B, H, T, _ = x_new.shape
     S_max = cache_nib.shape[2]
-    if cache_nib.shape != (B, H, S_max, _NBYTES_NIBBLE) or cache_qjl.shape != (B, H, S_max, _NBYTES_QJL) \
-            or cache_norms.shape != (B, H, S_max):
+    if (cache_qjl is None) != (cache_norms is None):
+        raise ValueError("cache_qjl and cache_norms must both be given or both be None")
+    if cache_nib.shape != (B, H, S_max, _NBYTES_NIBBLE) or (cache_qjl is not None and (
+            cache_qjl.shape != (B, H, S_max, _NBYTES_QJL) or cache_norms.shape != (B, H, S_max))):
         raise ValueError("cache tensors must be (B,H,S_max,64), (B,H,S_max,8), (B,H,S_max)")
-    if not (cache_nib.is_contiguous() and cache_qjl.is_contiguous() and cache_norms.is_contiguous()):
+    if not (cache_nib.is_contiguous() and (cache_qjl is None or (cache_qjl.is_contiguous() and cache_norms.is_contiguous()))):
         raise ValueError("cache tensors must be contiguous")
     if isinstance(offsets, torch.Tensor):
         if int(offsets.max()) + T > S_max or int(offsets.min()) < 0:

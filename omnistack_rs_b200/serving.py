@@ -48,6 +48,68 @@ def gather_rows_to_rank0(local: torch.Tensor, n_units: int, group=None) -> Optio
     return torch.cat([buf[: e - b] for buf, (b, e) in zip(bufs, spans)])
 
 
+class ShardLiveness:
+    """Host-side liveness record of the ranks of a sharded serving job, kept in a key-value store
+    (``torch.distributed.TCPStore`` or any object with ``set`` / ``get`` / ``check``).  The data path has no
+    collective, so a rank that stops cannot hang its peers; this record is how they learn of it before they next
+    depend on that rank (a verification gather, a barrier): every rank posts the number of the step it has
+    finished, and a rank that leaves on purpose says so.  Nothing here touches a GPU."""
+
+    def __init__(self, store, rank: int, world_size: int):
+        self.store, self.rank, self.world = store, rank, world_size
+
+    def beat(self, step: int) -> None:
+        self.store.set(f"omni/beat/{self.rank}", str(int(step)))
+
+    def leave(self) -> None:
+        self.store.set(f"omni/left/{self.rank}", "1")
+
+    def _step_of(self, r: int) -> int:
+        key = f"omni/beat/{r}"
+        return int(self.store.get(key)) if self.store.check([key]) else -1
+
+    def missing(self, step: int, timeout_s: float = 2.0, poll_s: float = 0.02):
+        """Ranks that have not finished ``step`` within ``timeout_s`` (or announced that they left)."""
+        import time
+        deadline = time.monotonic() + timeout_s
+        waiting = [r for r in range(self.world) if r != self.rank]
+        gone = []
+        while waiting:
+            for r in list(waiting):
+                if self.store.check([f"omni/left/{r}"]):
+                    waiting.remove(r); gone.append(r)
+                elif self._step_of(r) >= step:
+                    waiting.remove(r)
+            if not waiting or time.monotonic() >= deadline:
+                break
+            time.sleep(poll_s)
+        return sorted(gone + waiting)
+
+
+def collect_rows_via_store(store, rank: int, world_size: int, local: torch.Tensor, n_units: int, missing=()):
+    """Verification gather that survives absent ranks: every live rank posts its row block (sharded with
+    :func:`shard_range`) to the store and rank 0 assembles them.  Returns, on rank 0,
+    ``(rows, missing_spans)`` -- the ``(n_units, ...)`` tensor with the rows of absent ranks left at zero and
+    the ``[begin, end)`` unit ranges nobody delivered -- and ``None`` elsewhere."""
+    import io
+    if rank != 0:
+        buf = io.BytesIO()
+        torch.save(local.cpu(), buf)
+        store.set(f"omni/rows/{rank}", buf.getvalue())
+        return None
+    rows = local.new_zeros((n_units,) + tuple(local.shape[1:]), device="cpu")
+    b0, e0 = shard_range(n_units, world_size, 0)
+    rows[b0:e0] = local.cpu()
+    missing_spans = []
+    for r in range(1, world_size):
+        b, e = shard_range(n_units, world_size, r)
+        if r in missing:
+            missing_spans.append((b, e))
+            continue
+        rows[b:e] = torch.load(io.BytesIO(store.get(f"omni/rows/{r}")))
+    return rows, missing_spans
+
+
 class QuantizedKVCache:
     """Preallocated packed K/V cache for ``n_users`` users on one device.
 
@@ -66,7 +128,7 @@ class QuantizedKVCache:
         self.v_nib = mk(*shape, _NBYTES_NIBBLE)
         if store_v_residual:
             self.v_qjl, self.v_norms = mk(*shape, _NBYTES_QJL), mk(*shape, dt=torch.float32)
-        else:   # scratch rows shared by every append (attention never reads them)
+        else:   # attention never reads V's sign bits or norms: they are neither stored nor computed
             self.v_qjl = self.v_norms = None
         self.lens = torch.zeros(n_users, dtype=torch.int64, device=self.device)
         self.user_ids = (torch.arange(n_users, dtype=torch.int32, device=self.device) if user_ids is None
@@ -83,13 +145,8 @@ class QuantizedKVCache:
             raise ValueError("append would run past the cache capacity")
         rotate_quantize_append(k_new, self.k_nib, self.k_qjl, self.k_norms, self.lens, self.codebooks,
                                self.user_ids, rotate=rotate)
-        if self.v_qjl is not None:
-            rotate_quantize_append(v_new, self.v_nib, self.v_qjl, self.v_norms, self.lens, self.codebooks,
-                                   self.user_ids, rotate=rotate)
-        else:
-            vq = torch.empty(self.n_users, self.n_kv_heads, self.max_len, _NBYTES_QJL, dtype=torch.uint8, device=self.device)
-            vn = torch.empty(self.n_users, self.n_kv_heads, self.max_len, dtype=torch.float32, device=self.device)
-            rotate_quantize_append(v_new, self.v_nib, vq, vn, self.lens, self.codebooks, self.user_ids, rotate=rotate)
+        rotate_quantize_append(v_new, self.v_nib, self.v_qjl, self.v_norms, self.lens, self.codebooks,
+                               self.user_ids, rotate=rotate)
         self.lens += T
 
     def attend(self, q: torch.Tensor, scale: Optional[float] = None, with_qjl: bool = True,
@@ -154,5 +211,5 @@ class HostDecodeStep:
                 _lib.ptr(self.cb), self.per_head, _lib.ptr(self.ids), self.uid, _lib.ptr(self.lens), _lib.ptr(self.slots),
                 self.B, self.Hq, self.Hkv, self.T, self.S, self.Hkv * self.S, self.S, self.scale, self.with_qjl,
                 _lib.ptr(self.out_stage), _lib.ptr(self.out_host), self.n_chunks,
-                self.n_splits, _lib.ptr(self.ws), self.ws_bytes))
+                self.n_splits, _lib.ptr(self.ws), self.ws_bytes, _lib.ptr(_lib.status_word(self.dev))))
         return self.out_host

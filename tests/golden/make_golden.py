@@ -30,6 +30,7 @@ def sha(t) -> str:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
+    ap.add_argument("--only", nargs="*", default=None, help="write only these fixture files (default: all)")
     args = ap.parse_args()
     # Hide Triton so every reference routine takes its torch branch.
     sys.modules["triton"] = None
@@ -46,6 +47,8 @@ def main() -> None:
     here = os.path.dirname(os.path.abspath(__file__))
 
     def save(name, **arrs):
+        if args.only is not None and name not in args.only:
+            return
         out = {}
         for k, v in arrs.items():
             if isinstance(v, torch.Tensor):
@@ -150,6 +153,33 @@ def main() -> None:
                    x=xl, lora_a=la, lora_b=lb, lora_indices=lidx, lora_alpha=0.5)
     save("lora_attention.npz", k_nib=lkn, k_qjl=lkq, k_norms=lkr, v_nib=lvn, codebooks=cbl, user_id=np.array(2),
          q=ql, x=xl, lora_a=la, lora_b=lb, lora_indices=lidx, lora_alpha=np.array(0.5), q_eff=q_eff, out=ol)
+
+    # ---- row-seeded variant with row keys on both sides of 1,024 (seeds beyond the 1,024 per-head seeds)
+    g = torch.Generator().manual_seed(12)
+    xw = _wht_torch(torch.randn(3, 20, 128, generator=g))
+    wn, wq, wr = quantize_rows(xw, cbs[1], base_head_idx=1000, user_id=77)
+    what = dequantize_rows(wn, wq, wr, cbs[1], base_head_idx=1000, user_id=77, with_qjl=True)
+    save("rows_beyond_1024.npz", x=xw, codebook=cbs[1], base_head_idx=np.array(1000), user_id=np.array(77),
+         nib=wn, qjl=wq, norms=wr, x_hat=what)
+
+    # ---- attention over an UN-rotated cache with outlier channels: centroids far outside +-4, and queries aligned
+    #      with single keys so that one key dominates the softmax
+    g = torch.Generator().manual_seed(13)
+    B, Hq, Hkv, S = 2, 4, 2, 160
+    chans = torch.randperm(128, generator=g)[:4]
+    Kw = torch.randn(B, Hkv, S, 128, generator=g); Vw = torch.randn(B, Hkv, S, 128, generator=g)
+    Kw[..., chans] *= 8.0; Vw[..., chans] *= 8.0
+    cbw = calibrate_codebook(torch.cat([Kw.reshape(-1), Vw.reshape(-1)]))
+    wkn, wkq, wkr = quantize_heads(Kw, cbw, 11)
+    wvn, _, _ = quantize_heads(Vw, cbw, 11)
+    qw = torch.randn(B, Hq, 1, 128, generator=g) * 0.3
+    for b in range(B):
+        for h in range(Hq):
+            qw[b, h, 0] += 0.9 * Kw[b, h // (Hq // Hkv), 17 * (h + 1) + b]
+    qw = qw.to(torch.bfloat16)
+    ow = _fused_attn_python(qw.float(), wkn, wkq, wkr, wvn, cbw, 11, 1.0 / math.sqrt(128), True)
+    save("wide_codebook_attention.npz", codebook=cbw, user_id=np.array(11), k_nib=wkn, k_qjl=wkq, k_norms=wkr,
+         v_nib=wvn, q_bf16=qw, out=ow)
 
 
 if __name__ == "__main__":

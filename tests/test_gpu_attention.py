@@ -297,3 +297,67 @@ def test_dense_anchor_matches_oracle_and_packed_kernel(dev):
     assert (masked - short).abs().max() <= ATOL
     with pytest.raises(RuntimeError):
         reference_attn(q, k_hat, v_hat)
+
+
+def test_wide_codebook_with_peaked_softmax(dev, kernel_choice):
+    """Centroids out to +-20 (an un-rotated cache with outlier channels) and queries aligned with single keys,
+    so one key carries most of the softmax: fp16 centroids would be off by up to 2^-8 here.  Whichever kernel is
+    asked for, the call is served in fp32 (the tensor-core kernel stands down for such codebooks) and meets the
+    same 3e-3 as everywhere else.  Reference semantics: any fp32 codebook, kernels/quantize.py:620-636."""
+    fa = attn_mod()
+    g = load_golden("wide_codebook_attention.npz")
+    uid = int(g["user_id"])
+    cache = to_dev(dev, t(g["k_nib"]), t(g["k_qjl"]), t(g["k_norms"]), t(g["v_nib"]), t(g["codebook"]))
+    q = bf16(g["q_bf16"]).to(dev)
+    for ns in (None, 1, 3):
+        out = fa.omni_attn(q, *cache, user_id=uid, n_splits=ns)
+        assert (out.cpu() - t(g["out"])).abs().max() <= ATOL, ns
+    # per-head codebooks of which only the second is wide; long enough for the tensor-core kernel by itself
+    gen = torch.Generator().manual_seed(5)
+    B, Hq, Hkv, S = 2, 4, 2, 700
+    cb = torch.stack([torch.linspace(-2.5, 2.5, 16), torch.linspace(-19.0, 21.0, 16)])
+    K = torch.randn(B, Hkv, S, 128, generator=gen) * torch.tensor([1.0, 7.0]).view(1, 2, 1, 1)
+    V = torch.randn(B, Hkv, S, 128, generator=gen) * torch.tensor([1.0, 7.0]).view(1, 2, 1, 1)
+    kn, kq, kr = orc.quantize_heads(K, cb, 3)
+    vn, _, _ = orc.quantize_heads(V, cb, 3)
+    qq = (torch.randn(B, Hq, 1, 128, generator=gen) * 0.2 + K[:, :, 40].repeat_interleave(2, dim=1).unsqueeze(2) * 0.8).to(torch.bfloat16)
+    want = orc.decode_attention(qq, kn, kq, kr, vn, cb, 3)
+    assert float(want.abs().max()) > 5.0
+    got = fa.omni_attn(*to_dev(dev, qq, kn, kq, kr, vn, cb), user_id=3)
+    assert (got.cpu() - want).abs().max() <= ATOL
+
+
+def test_non_finite_centroid_is_reported(dev):
+    fa = attn_mod()
+    from omnistack_rs_b200 import _lib
+    kn, kq, kr, vn, cb, gen = make_cache(1, 1, 200, seed=6, per_head=False)
+    bad = cb.clone()
+    bad[15] = float("inf")
+    q = torch.randn(1, 1, 1, 128, generator=gen).to(torch.bfloat16)
+    fa.omni_attn(*to_dev(dev, q, kn, kq, kr, vn, bad), user_id=0)
+    with pytest.raises(NotImplementedError, match="centroid"):
+        _lib.check_device_status(dev)
+    _lib.check_device_status(dev)                                      # the word was cleared
+
+
+def test_bounded_wait_runs_out_and_is_reported(dev):
+    """Failure detection without a fault: a warp waits, with a limit of a few thousand polls, on an mbarrier that
+    nothing arrives on (the same wait routine guards the decode kernel's copies).  The wait must give up, the
+    kernel must return normally, the status word must say OMNI_STATUS_WAIT_EXPIRED and the host must raise; the
+    context stays usable afterwards."""
+    fa = attn_mod()
+    from omnistack_rs_b200 import _lib
+    lib = _lib.ensure_init(dev)
+    word = _lib.status_word(dev)
+    with torch.cuda.device(dev):
+        assert lib.omni_diag_bounded_wait(0, _lib.ptr(word), _lib.stream_ptr(dev)) == _lib.ERR_ARG
+        assert lib.omni_diag_bounded_wait(4096, None, _lib.stream_ptr(dev)) == _lib.ERR_ARG
+        assert lib.omni_diag_bounded_wait(4096, _lib.ptr(word), _lib.stream_ptr(dev)) == _lib.OK
+    torch.cuda.synchronize(dev)
+    assert int(word.item()) == 4
+    with pytest.raises(RuntimeError, match="bounded wait expired"):
+        _lib.check_device_status(dev)
+    kn, kq, kr, vn, cb, gen = make_cache(1, 1, 130, seed=2, per_head=False)
+    q = torch.randn(1, 1, 1, 128, generator=gen).to(torch.bfloat16)
+    out = fa.omni_attn(*to_dev(dev, q, kn, kq, kr, vn, cb), user_id=0)       # the device still works
+    assert (out.cpu() - orc.decode_attention(q, kn, kq, kr, vn, cb, 0)).abs().max() <= ATOL

@@ -126,8 +126,36 @@ def test_rows_variant(dev):
     assert torch.allclose(r_.cpu(), t(g["norms"]), rtol=NORM_RTOL)
     xh = quant.dequantize_rows(n_, q_, r_, t(g["codebook"]).to(dev), 3, 77, True)
     assert (xh.cpu() - t(g["x_hat"])).abs().max() <= DEQ_ATOL
-    with pytest.raises(NotImplementedError):
-        quant.quantize_rows(torch.zeros(8, 128, device=dev), t(g["codebook"]).to(dev), base_head_idx=1020)
+
+
+def test_rows_variant_beyond_1024_keys(dev):
+    """Row keys past 1,023 select MT19937 seeds above the 1,024 resident ones (the reference seeds one stream per
+    row for any row count, kernels/quantize.py:486-492, :524-535)."""
+    quant, _ = k()
+    g = load_golden("rows_beyond_1024.npz")
+    base, uid = int(g["base_head_idx"]), int(g["user_id"])
+    cb = t(g["codebook"]).to(dev)
+    n_, q_, r_ = quant.quantize_rows(t(g["x"]).to(dev), cb, base_head_idx=base, user_id=uid)
+    assert torch.equal(n_.cpu(), t(g["nib"])) and torch.equal(q_.cpu(), t(g["qjl"]))
+    assert torch.allclose(r_.cpu(), t(g["norms"]), rtol=NORM_RTOL)
+    xh = quant.dequantize_rows(n_, q_, r_, cb, base, uid, True)
+    assert (xh.cpu() - t(g["x_hat"])).abs().max() <= DEQ_ATOL
+    # an ordinary call of the reference's own tests: (2, 8, 100, 128) = 1,600 rows, keys 0..1599, two seed blocks
+    gen = torch.Generator().manual_seed(41)
+    x = orc.wht128(torch.randn(2, 8, 100, 128, generator=gen))
+    want = orc.quantize_rows(x, cb.cpu(), 0, 5)
+    got = quant.quantize_rows(x.to(dev), cb, 0, 5)
+    assert got[0].shape == (2, 8, 100, 64) and got[1].shape == (2, 8, 100, 8) and got[2].shape == (2, 8, 100)
+    assert torch.equal(got[0].cpu(), want[0]) and torch.equal(got[1].cpu(), want[1])
+    assert torch.allclose(got[2].cpu(), want[2], rtol=NORM_RTOL)
+    back = quant.dequantize_rows(*got, cb, 0, 5, True)
+    assert (back.cpu() - orc.dequantize_rows(*want, cb.cpu(), 0, 5, True)).abs().max() <= DEQ_ATOL
+    # a key range that starts in a third block and is revisited: the extended tables are rebuilt and reused
+    far = quant.quantize_rows(x[0, 0, :9].to(dev), cb, base_head_idx=5000, user_id=1029)
+    want_far = orc.quantize_rows(x[0, 0, :9], cb.cpu(), 5000, 1029)
+    assert torch.equal(far[1].cpu(), want_far[1])
+    again = quant.quantize_rows(x.to(dev), cb, 0, 5)
+    assert torch.equal(again[1].cpu(), want[1])
 
 
 @pytest.mark.parametrize("shape", [(1, 1, 1), (3, 2, 7), (2, 5, 33)])
@@ -231,6 +259,43 @@ def test_append_at_offsets(dev):
     assert int(cache.k_nib[:, :, 24:].max()) == 0          # rows past the length stay untouched
     with pytest.raises(ValueError):
         cache.append(torch.zeros(B, H, 17, 128, device=dev), torch.zeros(B, H, 17, 128, device=dev))
+
+
+def test_cache_without_v_residual_allocates_nothing_per_append(dev):
+    """A cache built with ``store_v_residual=False`` keeps no sign bits or norms for V (attention never reads
+    them): the V rows are produced without the projections, bit-equal to the full codec's nibbles, and an append
+    neither allocates scratch of the cache's extent nor moves the allocator's high-water mark."""
+    from omnistack_rs_b200.serving import QuantizedKVCache
+    gen = torch.Generator().manual_seed(10)
+    B, H, S_max = 4, 3, 96
+    cb = torch.sort(torch.randn(H, 16, generator=gen), dim=1).values
+    ids = torch.tensor([1, 2, 3, 2000], dtype=torch.int32)
+    cache = QuantizedKVCache(B, H, S_max, cb, dev, user_ids=ids, store_v_residual=False)
+    assert cache.v_qjl is None and cache.bytes_per_key() == 140
+    chunks = [(torch.randn(B, H, n, 128, generator=gen).to(torch.bfloat16).to(dev),
+               torch.randn(B, H, n, 128, generator=gen).to(torch.bfloat16).to(dev)) for n in (5, 8, 1, 30)]
+    cache.append(*chunks[0])
+    torch.cuda.synchronize(dev)
+    torch.cuda.reset_peak_memory_stats(dev)
+    before = torch.cuda.memory_allocated(dev)
+    for kc, vc in chunks[1:]:
+        cache.append(kc, vc)
+    torch.cuda.synchronize(dev)
+    assert torch.cuda.memory_allocated(dev) == before
+    assert torch.cuda.max_memory_allocated(dev) - before < 64 * 1024          # a few small index tensors at most
+    v_all = torch.cat([c[1] for c in chunks], dim=2).cpu()
+    k_all = torch.cat([c[0] for c in chunks], dim=2).cpu()
+    for b in range(B):
+        vn, _, _ = orc.rotate_quantize(v_all[b:b + 1], cb, int(ids[b]))
+        assert torch.equal(cache.v_nib[b, :, :44].cpu(), vn[0])
+        kn, kq, _ = orc.rotate_quantize(k_all[b:b + 1], cb, int(ids[b]))
+        assert torch.equal(cache.k_nib[b, :, :44].cpu(), kn[0]) and torch.equal(cache.k_qjl[b, :, :44].cpu(), kq[0])
+    q = torch.randn(B, 2 * H, 1, 128, generator=gen).to(torch.bfloat16)
+    out = cache.attend(q.to(dev)).cpu()
+    for b in range(B):
+        want = orc.decode_attention(q[b:b + 1], cache.k_nib[b:b + 1, :, :44].cpu(), cache.k_qjl[b:b + 1, :, :44].cpu(),
+                                    cache.k_norms[b:b + 1, :, :44].cpu(), cache.v_nib[b:b + 1, :, :44].cpu(), cb, int(ids[b]))
+        assert (out[b:b + 1] - want).abs().max() <= 3e-3
 
 
 def test_quantize_append_config3_slice_and_roundtrip(dev):

@@ -87,3 +87,50 @@ def test_box_serving_step_config4_batch():
     a = omni_attn(q[:256], kn, kq, kr, vn, cb, user_id=0, cache_slots=slots[:256], scale=0.05)
     b = omni_attn((q[:256].float() * 2).to(torch.bfloat16), kn, kq, kr, vn, cb, user_id=0, cache_slots=slots[:256], scale=0.025)
     assert (a - b).abs().max() <= 1e-3
+
+
+def test_gqa_decode_config2_full_size():
+    """Configuration 2 at its own size: 256 users, 32 query / 8 kv heads, context lengths
+    torch.randint(1024, 8193, (256,)) from seed 1, K/V N(0,1) with 4 channels x8 before the rotation, one shared
+    codebook fitted on a million rotated samples, the split count the library picks (ragged lengths: ticket
+    scheduling).  Oracle check on 10 users that include the shortest and the longest cache; the reference call is
+    kernels/fused_attention.py:435-466 on the same packed inputs."""
+    from omnistack_rs_b200.kernels.quantize import quantize_heads
+    from omnistack_rs_b200.kernels.hadamard import rotate_queries
+    from omnistack_rs_b200.kernels.fused_attention import omni_attn, _auto_splits
+    from omnistack_rs_b200.quantization import calibrate_codebook
+    from omnistack_rs_b200 import _lib
+    dev = torch.device("cuda:0")
+    B, Hq, Hkv, S = 256, 32, 8, 8192
+    lens = torch.randint(1024, 8193, (B,), generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    gen = torch.Generator(device=dev).manual_seed(2)
+    chans = torch.randperm(128, generator=torch.Generator().manual_seed(1))[:4].to(dev)
+    kn = torch.empty(B, Hkv, S, 64, dtype=torch.uint8, device=dev)
+    kq = torch.empty(B, Hkv, S, 8, dtype=torch.uint8, device=dev)
+    kr = torch.empty(B, Hkv, S, dtype=torch.float32, device=dev)
+    vn = torch.empty(B, Hkv, S, 64, dtype=torch.uint8, device=dev)
+    cb = None
+    for u0 in range(0, B, 32):
+        xk = torch.randn(32, Hkv, S, 128, generator=gen, device=dev)
+        xk[..., chans] *= 8.0
+        if cb is None:
+            cb = calibrate_codebook(rotate_queries(xk[:1]).reshape(-1)[: 1 << 20].contiguous())
+            assert float(cb.abs().max()) < 8.0            # after the rotation the outliers are spread out
+        kn[u0:u0 + 32], kq[u0:u0 + 32], kr[u0:u0 + 32] = quantize_heads(xk, cb, 0, rotate=True)
+        xv = torch.randn(32, Hkv, S, 128, generator=gen, device=dev)
+        xv[..., chans] *= 8.0
+        vn[u0:u0 + 32] = quantize_heads(xv, cb, 0, rotate=True)[0]
+        del xk, xv
+    q = torch.randn(B, Hq, 1, 128, generator=gen, device=dev, dtype=torch.bfloat16)
+    assert _auto_splits(B, Hq, Hkv, 1, S, True) > 1
+    out = omni_attn(q, kn, kq, kr, vn, cb, user_id=0, seq_lens=lens.to(dev))
+    _lib.check_device_status(dev)
+    assert out.shape == (B, Hq, 1, 128) and torch.isfinite(out).all()
+    one = omni_attn(q, kn, kq, kr, vn, cb, user_id=0, seq_lens=lens.to(dev), n_splits=1)
+    assert (out - one).abs().max() <= 1e-4                 # the split-K merge changes the last bits only
+    sample = sorted({int(lens.argmin()), int(lens.argmax()), 0, 1, 37, 100, 128, 200, 254, 255})
+    for u in sample:
+        n = int(lens[u])
+        want = orc.decode_attention(q[u:u + 1].cpu(), kn[u:u + 1, :, :n].cpu(), kq[u:u + 1, :, :n].cpu(),
+                                    kr[u:u + 1, :, :n].cpu(), vn[u:u + 1, :, :n].cpu(), cb.cpu(), 0)
+        assert (out[u:u + 1].cpu() - want).abs().max() <= 3e-3, (u, n)

@@ -178,12 +178,39 @@ def test_lora_golden():
 
 
 def test_lloyd_max_matches_stored_codebooks(config0_oracle):
+    """The oracle's fit on the samples the reference calibrated head 0 with (all 64 users x 50 tokens x 128 dims of
+    the rotated K) reproduces the codebook the reference stored, run to the reference's own 300-iteration cap."""
     g, cbs, Kr, _, _, _, _ = config0_oracle
-    fit = orc.lloyd_max_fit(Kr[:8, 3].reshape(-1))
+    fit = orc.lloyd_max_fit(Kr[:, 0].reshape(-1))
     assert fit.shape == (16,) and fit.dtype == torch.float32
     assert (fit[1:] >= fit[:-1]).all()
+    assert (fit - cbs[0]).abs().max() <= 1e-6
     with pytest.raises(ValueError):
         orc.lloyd_max_fit(torch.zeros(3))
+
+
+def test_rows_beyond_1024_golden():
+    """Row keys 1000..1059: the rows past key 1023 use MT19937 seeds above the 1,024 per-head seeds."""
+    g = load_golden("rows_beyond_1024.npz")
+    base, uid = int(g["base_head_idx"]), int(g["user_id"])
+    n_, q_, r_ = orc.quantize_rows(t(g["x"]), t(g["codebook"]), base_head_idx=base, user_id=uid)
+    assert torch.equal(n_, t(g["nib"])) and torch.equal(q_, t(g["qjl"]))
+    assert torch.allclose(r_, t(g["norms"]), rtol=5e-7, atol=0)
+    xh = orc.dequantize_rows(n_, q_, r_, t(g["codebook"]), base, uid, True)
+    assert (xh - t(g["x_hat"])).abs().max() <= 1e-6
+    for seed in (1024, 1500, 70000):                                  # G of large seeds against torch's CPU generator
+        gen = torch.Generator().manual_seed(seed)
+        bits = torch.randint(0, 2, (64, 128), generator=gen).numpy().astype(np.uint8)
+        assert np.array_equal(bits, orc.rademacher_bits(seed))
+
+
+def test_wide_codebook_attention_golden():
+    """Un-rotated cache with outlier channels (centroids out to +-20) and queries aligned with single keys."""
+    g = load_golden("wide_codebook_attention.npz")
+    assert float(np.abs(g["codebook"]).max()) > 16.0
+    out = orc.decode_attention(bf16(g["q_bf16"]), t(g["k_nib"]), t(g["k_qjl"]), t(g["k_norms"]), t(g["v_nib"]),
+                               t(g["codebook"]), int(g["user_id"]), None, True)
+    assert (out - t(g["out"])).abs().max() <= 2e-6
 
 
 def test_sign_ambiguity_is_rare(config0_oracle):
