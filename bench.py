@@ -52,6 +52,7 @@ WORKLOADS = {
 }
 BYTES_PER_KEY = 64 + 8 + 4 + 64          # K nibbles + K sign bytes + K norm + V nibbles
 FALLBACK_HBM_GBS = 6650.0
+PAIR_V = True          # the resident cache keeps V's nibble rows pair-wise (--v-layout reference: one key per row)
 # DRAM bytes per (user, kv head, key) of the decode kernel from its committed ncu capture summary;
 # scaled to a full launch by the keys it processes.
 NCU_DRAM_BYTES_PER_KEY = 150.0   # ncu capture of the decode kernel: (10.048 GB read + 0.020 GB written) / 67.1 M keys
@@ -117,8 +118,10 @@ def dist_env():
 
 def build_resident_cache(dev, Hkv, S, n_res, seed, lens=None):
     """Fill a resident packed cache with N(0,1) K/V pushed through the library's own
-    rotate+quantize kernel, chunk by chunk (set-up, untimed)."""
+    rotate+quantize kernel, chunk by chunk (set-up, untimed).  V's nibble rows are then put into the
+    pair layout of a serving cache (every complete group of eight keys below the user's length)."""
     from omnistack_rs_b200.kernels.quantize import _quantize_into
+    from omnistack_rs_b200.kernels.fused_attention import pair_v_rows
     gen = torch.Generator(device=dev).manual_seed(seed)
     cb = torch.tensor([-2.733, -2.069, -1.618, -1.256, -0.9424, -0.6568, -0.3881, -0.1284,
                        0.1284, 0.3881, 0.6568, 0.9424, 1.256, 1.618, 2.069, 2.733], device=dev)  # 16-level Lloyd-Max, unit Gaussian
@@ -135,6 +138,9 @@ def build_resident_cache(dev, Hkv, S, n_res, seed, lens=None):
         _quantize_into(x, cb, 0, True, k_nib[u0:u0 + n], k_qjl[u0:u0 + n], k_norms[u0:u0 + n], Hkv * S, S, None, 0)
         x = torch.randn(n, Hkv, S, 128, generator=gen, device=dev, dtype=torch.bfloat16)
         _quantize_into(x, cb, 0, True, v_nib[u0:u0 + n], sq[:n], sn[:n], Hkv * S, S, None, 0)
+    del sq, sn
+    if PAIR_V:
+        pair_v_rows(v_nib, 0, S if lens is None else lens.to(device=dev, dtype=torch.int64))
     torch.cuda.synchronize(dev)
     return k_nib, k_qjl, k_norms, v_nib, cb
 
@@ -152,6 +158,7 @@ def verify_against_oracle(dev, rank, world, users, Hq, q, out, k_nib, k_qjl, k_n
     the query they were computed from; rank 0 recomputes those users with the CPU oracle."""
     import torch.distributed as dist
     from omnistack_rs_b200.serving import gather_rows_to_rank0
+    from omnistack_rs_b200.kernels.fused_attention import pair_v_rows
     g = torch.Generator().manual_seed(100 + rank)
     picks = sorted({0, users - 1, *torch.randint(0, users, (max(n_check - 2, 0),), generator=g).tolist()})
     while len(picks) < min(n_check, users):
@@ -160,9 +167,12 @@ def verify_against_oracle(dev, rank, world, users, Hq, q, out, k_nib, k_qjl, k_n
     idx = torch.tensor(picks, device=dev)
     slot = idx if slots is None else slots[idx].long()
     S = k_nib.shape[2]
+    sample_lens = lens[idx].to(torch.int32) if lens is not None else torch.full((len(picks),), S, dtype=torch.int32, device=dev)
+    vn = v_nib[slot].contiguous()
+    if PAIR_V:
+        pair_v_rows(vn, 0, sample_lens.to(torch.int64))          # back to the reference layout the oracle reads
     sample = {"out": out[idx].float(), "q": q[idx], "kn": k_nib[slot], "kq": k_qjl[slot],
-              "kr": k_norms[slot], "vn": v_nib[slot],
-              "len": (lens[idx].to(torch.int32) if lens is not None else torch.full((len(picks),), S, dtype=torch.int32, device=dev))}
+              "kr": k_norms[slot], "vn": vn, "len": sample_lens}
     checksum = out.float().sum(dim=(1, 2, 3)).unsqueeze(1)                      # one number per user
     if world > 1:
         sample = {k: gather_rows_to_rank0(v.contiguous(), len(picks) * world) for k, v in sample.items()}
@@ -208,7 +218,9 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
     if workload == "gqa":
         g = torch.Generator().manual_seed(1)
         lens = torch.randint(1024, 8193, (users,), generator=g).to(torch.int32)
-    k_nib, k_qjl, k_norms, v_nib, cb = build_resident_cache(dev, Hkv, S, n_res, seed=1234 + rank)
+    if lens is not None and n_res < users:
+        raise SystemExit("ragged lengths need every user resident (the pair layout of V follows each user's length)")
+    k_nib, k_qjl, k_norms, v_nib, cb = build_resident_cache(dev, Hkv, S, n_res, seed=1234 + rank, lens=lens)
     slots = (torch.arange(users, dtype=torch.int32) % n_res).to(dev) if n_res < users else None
     lens_dev = None if lens is None else lens.to(dev)
     keys_per_step = int(lens.sum()) * Hkv if lens is not None else users * Hkv * S
@@ -220,7 +232,7 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
 
     def step(i):
         return _qattn(qs[i % n_q], k_nib, k_qjl, k_norms, v_nib, cb, 0, scale, True,
-                      seq_lens=lens_dev, cache_slots=slots, n_splits=n_splits)
+                      seq_lens=lens_dev, cache_slots=slots, n_splits=n_splits, v_paired=PAIR_V)
 
     def barrier():
         if world > 1:
@@ -266,7 +278,7 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
     # ---- end to end: host query in, host result out -----------------------------------
     host = HostDecodeStep(k_nib, k_qjl, k_norms, v_nib, cb, n_heads=Hq, batch=users, q_dtype=torch.bfloat16,
                           user_id=0, seq_lens=lens_dev, cache_slots=slots, scale=scale,
-                          n_chunks=args.chunks if workload == args.workload else None)
+                          n_chunks=args.chunks if workload == args.workload else None, v_paired=PAIR_V)
     host.q_host.copy_(qs[0].cpu())
     for _ in range(max(1, min(warmup, 3))):
         host.step()
@@ -284,7 +296,7 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_s_step = float(e2e_t) / e2e_steps
     ref_out = _qattn(qs[0], k_nib, k_qjl, k_norms, v_nib, cb, 0, scale, True,
-                     seq_lens=lens_dev, cache_slots=slots, n_splits=1)
+                     seq_lens=lens_dev, cache_slots=slots, n_splits=1, v_paired=PAIR_V)
     e2e_ok = bool((res - ref_out.cpu()).abs().max() <= 1.5e-3)   # splits round their fp16 softmax weights against other maxima
     _lib.check_device_status(dev)
 
@@ -307,6 +319,7 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "dtype_note": "f16 tensor-core operands (s8 for the sign term), f32 accumulation and softmax", "data": "synthetic",
         "config": {"workload": desc, "users_per_gpu": users, "resident_users": n_res, "q_heads": Hq, "kv_heads": Hkv,
                    "keys": S, "head_dim": 128, "bytes_per_key": BYTES_PER_KEY, "splits": n_splits,
+                   "v_layout": "pair" if PAIR_V else "reference",
                    "l2": ("L2 flushed between timed steps (a 192 MiB buffer is written before each)" if small else
                           "inputs larger than L2 (resident cache %.1f GB per GPU)" % (n_res * bytes_per_user / 1e9)),
                    "parallelism": f"users sharded over {world} GPU(s), no collective on the data path"},
@@ -695,7 +708,11 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="default workload only: skip the other configurations")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--ref-users", type=int, default=2, help="users per step of the reference arm")
+    ap.add_argument("--v-layout", default="pair", choices=["pair", "reference"],
+                    help="layout of V's nibble rows in the resident cache (pair: the serving cache's own format)")
     args = ap.parse_args()
+    global PAIR_V
+    PAIR_V = args.v_layout == "pair"
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

@@ -152,6 +152,10 @@ int32_t omni_dequantize_rows(const uint8_t* nib, const uint8_t* qjl, const float
  *   rotate_q / unrotate_out  fold the Walsh-Hadamard rotation into the query /
  *                out of the result (both 0 reproduces the reference, which expects a
  *                rotated q and returns the output in rotated space)
+ *   v_paired     0: v_nib is in the reference layout.  1: it is in the pair layout that
+ *                omni_v_pair_groups produces, for every group of eight keys that lies completely
+ *                below the user's length (seq_lens[b], or S); the user's last, incomplete group
+ *                is in the reference layout.  Same results, fewer instructions per key.
  *   n_splits     >= 1 partitions of the key axis; with n_splits > 1 `workspace` must
  *                hold omni_qattn_workspace_bytes(...) bytes of device scratch
  *   out          device fp32 [B][Hq][T][128]
@@ -173,9 +177,22 @@ int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
                           const int32_t* seq_lens, const int32_t* cache_slots,
                           int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                           int64_t ks_b, int64_t ks_h,
-                          float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out,
+                          float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out, int32_t v_paired,
                           int32_t n_splits, void* workspace, size_t workspace_bytes,
                           float* out, int32_t* status_word, void* stream);
+
+/* Pair layout of the V nibble rows of a resident cache (no counterpart in the reference, whose tensors keep one
+ * key per row; this is an internal format of a cache that this library appends to and reads).  The tensor-core
+ * kernel's P.V product pairs two keys per operand register, so its table index is (nibble of key a) | (nibble of
+ * key b) << 4.  Within each group of eight consecutive keys the pairs are (0,3), (1,2), (4,7), (5,6); the row of a
+ * pair's first key receives byte j = code[a][2j] | code[b][2j] << 4 (even dims of both keys), the row of its
+ * second key the odd dims.  The call converts, in place, the groups that became complete when a user's length
+ * grew from lens_before[b] to lens_after[b] (device int64 [B]; or the scalars len_before / len_after when the
+ * arrays are NULL): groups [before / 8, after / 8).  Applying it twice restores the reference layout.  Rows as in
+ * omni_qattn_decode: (b, h, s) at b*ks_b + h*ks_h + s, S keys of capacity per (b, h). */
+int32_t omni_v_pair_groups(uint8_t* v_nib, int64_t B, int32_t H, int64_t S, int64_t ks_b, int64_t ks_h,
+                           const int64_t* lens_before, int64_t len_before,
+                           const int64_t* lens_after, int64_t len_after, void* stream);
 
 /* Per-user low-rank query update ahead of attention (kernels/fused_attention.py:166-191 fused prologue,
  * :401-430 `_apply_lora_to_q`): out[b,h,t,:] = q[b,h,t,:] + alpha * ((x[b,t,:] A[i]^T) B[i]^T)[h,:] with
@@ -211,7 +228,7 @@ int32_t omni_qattn_decode_lora(const void* q, int32_t q_dtype,
                                const int32_t* seq_lens, const int32_t* cache_slots,
                                int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                                int64_t ks_b, int64_t ks_h,
-                               float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out,
+                               float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out, int32_t v_paired,
                                int32_t n_splits, void* workspace, size_t workspace_bytes,
                                float* out, int32_t* status_word, void* stream, const omni_lora_t* lora);
 
@@ -249,7 +266,7 @@ int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
                                   const int32_t* seq_lens, const int32_t* cache_slots,
                                   int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                                   int64_t ks_b, int64_t ks_h,
-                                  float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out,
+                                  float scale, int32_t with_qjl, int32_t rotate_q, int32_t unrotate_out, int32_t v_paired,
                                   int32_t n_splits, float* out, void* stream);
 /* Reads the status word of the allocation-free entry point on the current device into *value_out (0 = nothing
  * to report, else an OMNI_STATUS_* value) and, with clear != 0, resets it.  Waits for the device first. */
@@ -277,7 +294,7 @@ int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, void* q_stag
                                const int32_t* seq_lens, const int32_t* cache_slots,
                                int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                                int64_t ks_b, int64_t ks_h,
-                               float scale, int32_t with_qjl,
+                               float scale, int32_t with_qjl, int32_t v_paired,
                                float* out_stage, float* out_host, int32_t n_chunks,
                                int32_t n_splits, void* workspace, size_t workspace_bytes,
                                int32_t* status_word);

@@ -33,12 +33,13 @@ SIGNATURES = {
     "omni_dequantize_rows": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp]),
     "omni_qattn_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32]),
     "omni_qattn_decode": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
-                                 _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
+                                 _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32, _i32,
                                  _vp, _sz, _vp, _vp, _vp]),
+    "omni_v_pair_groups": (_i32, [_vp, _i64, _i32, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
     "omni_lora_q": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _f32, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "omni_qattn_lora_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32]),
     "omni_qattn_decode_lora": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
-                                      _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
+                                      _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32, _i32,
                                       _vp, _sz, _vp, _vp, _vp, _vp]),
     "omni_qjl_encode_bool": (_i32, [_vp, _i64, _i32, _vp, _vp, _vp]),
     "omni_qjl_reconstruct_bool": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
@@ -46,10 +47,10 @@ SIGNATURES = {
     "omni_lloyd_max_fit": (_i32, [_vp, _i64, _vp, _i32, _i32, C.c_double, _vp, _sz, _vp, _vp, _vp]),
     "omni_qattn_noalloc_scratch_bytes": (_sz, []),
     "omni_qattn_decode_noalloc": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
-                                         _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
+                                         _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32, _i32,
                                          _vp, _vp]),
     "omni_qattn_decode_host": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp,
-                                      _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _vp, _vp, _i32,
+                                      _i64, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _i32, _i32, _vp, _vp, _i32,
                                       _i32, _vp, _sz, _vp]),
     "omni_qattn_noalloc_status": (_i32, [_vp, _i32]),
     "omni_diag_bounded_wait": (_i32, [_i32, _vp, _vp]),

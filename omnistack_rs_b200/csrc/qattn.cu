@@ -142,17 +142,41 @@ __global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(Att
             m = m_new;
         }
         l += p;
-        const uint4* vp = reinterpret_cast<const uint4*>(a.v_nib + row * kNibBytes);
+        if (a.v_paired && k < (len & ~(int64_t)7)) {
+            // pair layout: this key's even-d nibbles sit in the row of the pair's first key, its odd-d nibbles in
+            // the row of the second (pairs (0,3), (1,2), (4,7), (5,6) of a group of eight: partner = key ^ 3), in
+            // the low nibbles when this key is the first of the pair, else in the high ones
+            const int64_t first = (k & 2) ? (k ^ 3) : k;
+            const int sh = (k & 2) ? 4 : 0;
+            const uint4* xp = reinterpret_cast<const uint4*>(a.v_nib + (base_row + first) * kNibBytes);
+            const uint4* yp = reinterpret_cast<const uint4*>(a.v_nib + (base_row + (first ^ 3)) * kNibBytes);
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-            const uint4 wv = __ldg(vp + c4);
-            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+            for (int c4 = 0; c4 < 4; ++c4) {
+                const uint4 xv = __ldg(xp + c4), yv = __ldg(yp + c4);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, yw[4] = {yv.x, yv.y, yv.z, yv.w};
 #pragma unroll
-            for (int wi = 0; wi < 4; ++wi) {
-                const uint32_t w = ww[wi];
+                for (int wi = 0; wi < 4; ++wi) {
 #pragma unroll
-                for (int n = 0; n < 8; ++n)
-                    O[c4 * 32 + wi * 8 + n] = fmaf(p, cbs[(w >> (4 * n)) & 15], O[c4 * 32 + wi * 8 + n]);
+                    for (int i = 0; i < 4; ++i) {
+                        const int d = c4 * 32 + wi * 8 + 2 * i;
+                        O[d] = fmaf(p, cbs[(xw[wi] >> (8 * i + sh)) & 15], O[d]);
+                        O[d + 1] = fmaf(p, cbs[(yw[wi] >> (8 * i + sh)) & 15], O[d + 1]);
+                    }
+                }
+            }
+        } else {
+            const uint4* vp = reinterpret_cast<const uint4*>(a.v_nib + row * kNibBytes);
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+                const uint4 wv = __ldg(vp + c4);
+                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+                    const uint32_t w = ww[wi];
+#pragma unroll
+                    for (int n = 0; n < 8; ++n)
+                        O[c4 * 32 + wi * 8 + n] = fmaf(p, cbs[(w >> (4 * n)) & 15], O[c4 * 32 + wi * 8 + n]);
+                }
             }
         }
     }
@@ -245,6 +269,39 @@ __global__ void __launch_bounds__(kCombineWarps * 32) qattn_combine_kernel(const
     *reinterpret_cast<float4*>(out + r * kHeadDim + 4 * lane) = make_float4(o[0], o[1], o[2], o[3]);
 }
 
+
+// Pair layout of V nibble rows.  In the tensor-core kernel the V operand of the P.V product pairs two KEYS per
+// register, so its table index is (nibble of key a) | (nibble of key b) << 4; a cache that stores exactly those bytes
+// saves the shift-and-merge per lookup.  Within a group of eight consecutive keys the pairs are (0,3), (1,2), (4,7),
+// (5,6); the row of the pair's first key receives the even-d nibbles of both keys (byte j = code[a][2j] |
+// code[b][2j] << 4), the row of the second key the odd-d nibbles.  The transform is its own inverse.  One warp
+// converts one group: lane = (pair, 8-byte column).
+__global__ void __launch_bounds__(256) v_pair_groups_kernel(uint8_t* v_nib, int64_t B, int H, int64_t ks_b, int64_t ks_h,
+                                                            const int64_t* lens_before, int64_t len_before,
+                                                            const int64_t* lens_after, int64_t len_after, int64_t max_groups) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = (int64_t)gridDim.x * 8;
+    const int64_t units = B * H * max_groups;
+    for (int64_t u = warp; u < units; u += n_warps) {
+        const int64_t gi = u % max_groups, bh = u / max_groups;
+        const int h = (int)(bh % H);
+        const int64_t b = bh / H;
+        const int64_t g0 = (lens_before ? lens_before[b] : len_before) >> 3, g1 = (lens_after ? lens_after[b] : len_after) >> 3;
+        const int64_t grp = g0 + gi;                    // groups [g0, g1) became complete with this append
+        if (grp >= g1) continue;
+        const int pair = lane >> 3, col = lane & 7;
+        const int ra = (pair & 1) + 4 * (pair >> 1), rb = ra ^ 3;            // rows 0,1,4,5 and their partners 3,2,7,6
+        uint8_t* base = v_nib + (b * ks_b + (int64_t)h * ks_h + grp * 8) * kNibBytes + 8 * col;
+        uint2* pa = reinterpret_cast<uint2*>(base + ra * kNibBytes);
+        uint2* pb = reinterpret_cast<uint2*>(base + rb * kNibBytes);
+        const uint2 A = *pa, Bv = *pb;
+        uint2 x, y;
+        x.x = (A.x & 0x0F0F0F0Fu) | ((Bv.x << 4) & 0xF0F0F0F0u);  y.x = ((A.x >> 4) & 0x0F0F0F0Fu) | (Bv.x & 0xF0F0F0F0u);
+        x.y = (A.y & 0x0F0F0F0Fu) | ((Bv.y << 4) & 0xF0F0F0F0u);  y.y = ((A.y >> 4) & 0x0F0F0F0Fu) | (Bv.y & 0xF0F0F0F0u);
+        *pa = x;
+        *pb = y;
+    }
+}
 
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
@@ -383,14 +440,14 @@ extern "C" int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
                                      const int32_t* seq_lens, const int32_t* cache_slots,
                                      int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                                      int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
-                                     int32_t rotate_q, int32_t unrotate_out, int32_t n_splits,
+                                     int32_t rotate_q, int32_t unrotate_out, int32_t v_paired, int32_t n_splits,
                                      void* workspace, size_t workspace_bytes, float* out,
                                      int32_t* status_word, void* stream) {
     const DeviceTables* tb = tables_for_current_device();
     if (!tb) return OMNI_ERR_NOT_INIT;
     AttnArgs a{q, q_dtype, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id, seq_lens,
                cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
-               (float*)workspace, out, tb->rows, status_word};
+               (float*)workspace, out, tb->rows, status_word, nullptr, v_paired};
     int32_t st = validate(a, workspace_bytes);
     if (st != OMNI_OK) return st;
     return launch(a, (cudaStream_t)stream);
@@ -412,13 +469,13 @@ extern "C" int32_t omni_qattn_decode_lora(const void* q, int32_t q_dtype,
                                           const int32_t* seq_lens, const int32_t* cache_slots,
                                           int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                                           int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
-                                          int32_t rotate_q, int32_t unrotate_out, int32_t n_splits,
+                                          int32_t rotate_q, int32_t unrotate_out, int32_t v_paired, int32_t n_splits,
                                           void* workspace, size_t workspace_bytes, float* out,
                                           int32_t* status_word, void* stream, const omni_lora_t* lora) {
     if (!lora)
         return omni_qattn_decode(q, q_dtype, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id,
                                  seq_lens, cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q,
-                                 unrotate_out, n_splits, workspace, workspace_bytes, out, status_word, stream);
+                                 unrotate_out, v_paired, n_splits, workspace, workspace_bytes, out, status_word, stream);
     const DeviceTables* tb = tables_for_current_device();
     if (!tb) return OMNI_ERR_NOT_INIT;
     const size_t qb = lora_q_bytes(B, Hq, T);
@@ -428,7 +485,7 @@ extern "C" int32_t omni_qattn_decode_lora(const void* q, int32_t q_dtype,
     float* q_eff = (float*)workspace;
     AttnArgs a{q_eff, OMNI_F32, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id, seq_lens,
                cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
-               (float*)((char*)workspace + qb), out, tb->rows, status_word};
+               (float*)((char*)workspace + qb), out, tb->rows, status_word, nullptr, v_paired};
     int32_t st = validate(a, workspace_bytes - (B == 0 || T == 0 ? 0 : qb));
     if (st != OMNI_OK) return st;
     OMNI_REQUIRE(q, OMNI_ERR_ARG, "qattn_decode_lora: NULL q");
@@ -444,7 +501,7 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
                                           const int32_t* user_ids, int32_t user_id,
                                           const int32_t* seq_lens, const int32_t* cache_slots,
                                           int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
-                                          int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
+                                          int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl, int32_t v_paired,
                                           float* out_stage, float* out_host, int32_t n_chunks,
                                           int32_t n_splits, void* workspace, size_t workspace_bytes,
                                           int32_t* status_word) {
@@ -486,7 +543,7 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
                    seq_lens ? seq_lens + b0 : nullptr, cache_slots ? cache_slots + b0 : nullptr,
                    nb, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, 0, 0, n_splits,
                    n_splits > 1 ? reinterpret_cast<float*>((char*)workspace + (size_t)(c & 1) * ws_chunk) : nullptr,
-                   out_stage + qoff, tb->rows, status_word};
+                   out_stage + qoff, tb->rows, status_word, nullptr, v_paired};
         int32_t stc = validate(a, ws_chunk);
         if (stc == OMNI_OK) stc = launch(a, st);
         if (stc != OMNI_OK) { cudaStreamSynchronize(g_hs[dev].s[0]); cudaStreamSynchronize(g_hs[dev].s[1]); return stc; }
@@ -498,6 +555,26 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
     return OMNI_OK;
 }
 
+extern "C" int32_t omni_v_pair_groups(uint8_t* v_nib, int64_t B, int32_t H, int64_t S, int64_t ks_b, int64_t ks_h,
+                                      const int64_t* lens_before, int64_t len_before,
+                                      const int64_t* lens_after, int64_t len_after, void* stream) {
+    OMNI_REQUIRE(B >= 0 && H >= 0 && S >= 0, OMNI_ERR_ARG, "omni_v_pair_groups: negative extent");
+    OMNI_REQUIRE((lens_before == nullptr) == (lens_after == nullptr), OMNI_ERR_ARG,
+                 "omni_v_pair_groups: give both length arrays or neither");
+    if (!lens_before) {
+        OMNI_REQUIRE(0 <= len_before && len_before <= len_after && len_after <= S, OMNI_ERR_ARG,
+                     "omni_v_pair_groups: lengths %lld -> %lld outside [0, %lld]", (long long)len_before, (long long)len_after, (long long)S);
+    }
+    const int64_t max_groups = lens_before ? (S >> 3) : ((len_after >> 3) - (len_before >> 3));
+    if (B == 0 || H == 0 || max_groups <= 0) return OMNI_OK;
+    OMNI_REQUIRE(v_nib && aligned(v_nib, 8), OMNI_ERR_ARG, "omni_v_pair_groups: NULL or misaligned nibble array");
+    int64_t blocks = (B * H * max_groups + 7) / 8;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    v_pair_groups_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(v_nib, B, H, ks_b, ks_h, lens_before, len_before,
+                                                                           lens_after, len_after, max_groups);
+    return check_cuda(cudaGetLastError(), "v_pair_groups_kernel launch");
+}
+
 extern "C" size_t omni_qattn_noalloc_scratch_bytes(void) { return kStaticScratchBytes; }
 
 extern "C" int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
@@ -507,7 +584,7 @@ extern "C" int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
                                              const int32_t* seq_lens, const int32_t* cache_slots,
                                              int64_t B, int32_t Hq, int32_t Hkv, int32_t T, int64_t S,
                                              int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
-                                             int32_t rotate_q, int32_t unrotate_out, int32_t n_splits,
+                                             int32_t rotate_q, int32_t unrotate_out, int32_t v_paired, int32_t n_splits,
                                              float* out, void* stream) {
     const size_t need = omni_qattn_workspace_bytes(B, Hq, T, n_splits);
     OMNI_REQUIRE(need <= kStaticScratchBytes, OMNI_ERR_UNSUPPORTED,
@@ -519,7 +596,7 @@ extern "C" int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
     if (st != OMNI_OK) return st;
     AttnArgs a{q, q_dtype, k_nib, k_qjl, k_norms, v_nib, codebooks, cb_per_head, user_ids, user_id, seq_lens,
                cache_slots, B, Hq, Hkv, T, S, ks_b, ks_h, scale, with_qjl, rotate_q, unrotate_out, n_splits,
-               arr.scratch, out, arr.rows, arr.status};
+               arr.scratch, out, arr.rows, arr.status, nullptr, v_paired};
     st = validate(a, kStaticScratchBytes);
     if (st != OMNI_OK) return st;
     return launch(a, (cudaStream_t)stream);

@@ -16,6 +16,9 @@ struct AttnArgs {
     int32_t* status;           // device word set non-zero when a bounded wait expires (may be null)
     uint32_t* work_counter;    // kWorkCounterBytes of device memory behind the split-K partials: one ticket counter
                                // per kv head for the tensor-core kernel (null: items are assigned statically)
+    int v_paired;              // V nibble rows are stored pair-wise (see omni_v_pair_groups): within every group of eight
+                               // keys that lies completely below the user's length, the rows of keys (0,3), (1,2), (4,7),
+                               // (5,6) hold the even-d / odd-d nibbles of both keys instead of one key's 128 nibbles each
     int only_if_wide;          // lane-per-key kernel: 1 = run only when the codebooks are outside the fp16 table's
                                // range (it then completes a call whose tensor-core launch stood down), 0 = always
 };

@@ -207,7 +207,9 @@ __device__ __forceinline__ int rho8(int r) { return (0x65742130 >> (4 * r)) & 7;
 
 struct KeyBlock {           // packed bytes of one 16-key block as this thread needs them
     uint4 ka, kb;           // K nibbles: keys rho(g) and rho(g)+8, bytes 16t..16t+15
-    uint2 v0, v1, v2, v3;   // V nibbles: keys rho(2t), rho(2t+1), rho(2t)+8, rho(2t+1)+8, bytes 8g..8g+7
+    uint2 v0, v1, v2, v3;   // V nibbles, bytes 8g..8g+7.  Reference layout: rows of keys rho(2t), rho(2t+1), rho(2t)+8,
+                            // rho(2t+1)+8.  Pair layout (VPAIR): v0 / v1 = even-d / odd-d nibbles of the key pair
+                            // (rho(2t), rho(2t+1)), low nibble = first key; v2 / v3 the same eight keys further on
     uint32_t sa, sb;        // K sign bits: keys rho(g), rho(g)+8, bits 16t..16t+15
     float na, nb;           // K residual norms: keys rho(g), rho(g)+8
 };
@@ -223,17 +225,30 @@ __device__ __forceinline__ void load_aux(AuxRegs& x, const uint8_t* ps, const fl
 
 // Partial last block, read with plain loads: rows past the end are clamped to the last valid key
 // (their scores are masked).  row0 = first row of the block in the packed arrays.
-template <bool QJL>
-__device__ __forceinline__ void load_tail_block(KeyBlock& kb, const AttnArgs& a, int64_t row0, int nvalid,
+// two rows of the reference layout -> the pair layout of the same 16 nibble columns
+__device__ __forceinline__ void pair_rows(uint2& x, uint2& y) {
+    const uint2 A = x, B = y;
+    x.x = (A.x & 0x0F0F0F0Fu) | ((B.x << 4) & 0xF0F0F0F0u);  y.x = ((A.x >> 4) & 0x0F0F0F0Fu) | (B.x & 0xF0F0F0F0u);
+    x.y = (A.y & 0x0F0F0F0Fu) | ((B.y << 4) & 0xF0F0F0F0u);  y.y = ((A.y >> 4) & 0x0F0F0F0Fu) | (B.y & 0xF0F0F0F0u);
+}
+
+// `paired_rows` (0, 8 or 16; VPAIR only): how many rows from row0 on are stored in the pair layout -- the groups of
+// eight keys that lie completely below the user's length.  The block comes out in the layout the template says:
+// with VPAIR the groups still in the reference layout (the user's last, incomplete group) are paired here.
+template <bool QJL, bool VPAIR>
+__device__ __forceinline__ void load_tail_block(KeyBlock& kb, const AttnArgs& a, int64_t row0, int nvalid, int paired_rows,
                                                 int kr, int va, int vb, int g, int t) {
     const int last = nvalid - 1;
     const int64_t rk = row0 + min(kr, last), rk8 = row0 + min(kr + 8, last);
     kb.ka = ldg_stream16(a.k_nib + rk * kNibBytes + 16 * t);
     kb.kb = ldg_stream16(a.k_nib + rk8 * kNibBytes + 16 * t);
-    kb.v0 = ldg_stream8(a.v_nib + (row0 + min(va, last)) * kNibBytes + 8 * g);
-    kb.v1 = ldg_stream8(a.v_nib + (row0 + min(vb, last)) * kNibBytes + 8 * g);
-    kb.v2 = ldg_stream8(a.v_nib + (row0 + min(va + 8, last)) * kNibBytes + 8 * g);
-    kb.v3 = ldg_stream8(a.v_nib + (row0 + min(vb + 8, last)) * kNibBytes + 8 * g);
+    const bool p0 = VPAIR && paired_rows >= 8, p1 = VPAIR && paired_rows >= 16;      // stored pair-wise: every row exists
+    kb.v0 = ldg_stream8(a.v_nib + (row0 + (p0 ? va : min(va, last))) * kNibBytes + 8 * g);
+    kb.v1 = ldg_stream8(a.v_nib + (row0 + (p0 ? vb : min(vb, last))) * kNibBytes + 8 * g);
+    kb.v2 = ldg_stream8(a.v_nib + (row0 + (p1 ? va + 8 : min(va + 8, last))) * kNibBytes + 8 * g);
+    kb.v3 = ldg_stream8(a.v_nib + (row0 + (p1 ? vb + 8 : min(vb + 8, last))) * kNibBytes + 8 * g);
+    if (VPAIR && !p0) pair_rows(kb.v0, kb.v1);
+    if (VPAIR && !p1) pair_rows(kb.v2, kb.v3);
     if (QJL) {
         kb.sa = ldg_stream2(a.k_qjl + rk * kQjlBytes + 2 * t);
         kb.sb = ldg_stream2(a.k_qjl + rk8 * kQjlBytes + 2 * t);
@@ -252,7 +267,7 @@ constexpr float kLazyMaxSlack = 6.f;   // log2 units a score may exceed the refe
 
 // ONECOL: the kv head has a single query column (plain decode without query grouping).  Only column 0 of the
 // score tile is real then, so the scalar softmax work of the second column of every lane is left out.
-template <bool QJL, bool TAIL, bool ONECOL>
+template <bool QJL, bool TAIL, bool ONECOL, bool VPAIR>
 __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState& st, const uint32_t (&qB)[8][2],
                                                   const SignB& sg, float post0, float post1,
                                                   uint32_t lut_lane, int nvalid, int kl) {
@@ -332,16 +347,16 @@ __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState&
     // P^T as the B operand: transpose the two 8x8 (key x column) blocks across the warp
     const uint32_t pb0 = movmatrix_trans(pack_half2(p00, p01));
     const uint32_t pb1 = movmatrix_trans(pack_half2(p80, p81));
-    // V: index byte = nibble of key A | nibble of key B << 4
+    // V: index byte = nibble of key A | nibble of key B << 4 (the pair layout stores exactly these bytes)
     {
         const uint32_t A[2] = {kb.v0.x, kb.v0.y}, B[2] = {kb.v1.x, kb.v1.y};
         const uint32_t C[2] = {kb.v2.x, kb.v2.y}, D[2] = {kb.v3.x, kb.v3.y};
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t x01 = (A[h] & 0x0F0F0F0Fu) | ((B[h] << 4) & 0xF0F0F0F0u);
-            const uint32_t y01 = ((A[h] >> 4) & 0x0F0F0F0Fu) | (B[h] & 0xF0F0F0F0u);
-            const uint32_t x23 = (C[h] & 0x0F0F0F0Fu) | ((D[h] << 4) & 0xF0F0F0F0u);
-            const uint32_t y23 = ((C[h] >> 4) & 0x0F0F0F0Fu) | (D[h] & 0xF0F0F0F0u);
+            const uint32_t x01 = VPAIR ? A[h] : (A[h] & 0x0F0F0F0Fu) | ((B[h] << 4) & 0xF0F0F0F0u);
+            const uint32_t y01 = VPAIR ? B[h] : ((A[h] >> 4) & 0x0F0F0F0Fu) | (B[h] & 0xF0F0F0F0u);
+            const uint32_t x23 = VPAIR ? C[h] : (C[h] & 0x0F0F0F0Fu) | ((D[h] << 4) & 0xF0F0F0F0u);
+            const uint32_t y23 = VPAIR ? D[h] : ((C[h] >> 4) & 0x0F0F0F0Fu) | (D[h] & 0xF0F0F0F0u);
             mma_f16(st.O[4 * h + 0], lut_at<0>(lut_lane, x01), lut_at<0>(lut_lane, y01),
                                      lut_at<0>(lut_lane, x23), lut_at<0>(lut_lane, y23), pb0, pb1);
             mma_f16(st.O[4 * h + 1], lut_at<1>(lut_lane, x01), lut_at<1>(lut_lane, y01),
@@ -383,7 +398,7 @@ __device__ __forceinline__ void ring_consumed(Ring& r) {
     --r.in_flight;
 }
 
-template <int DT, bool QJL, bool ONECOL>
+template <int DT, bool QJL, bool ONECOL, bool VPAIR>
 __global__ void __launch_bounds__(kMmaWarps * 32, 1)
 qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v) {
@@ -660,8 +675,8 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
                     load_aux(aux_b, ps + 16 * kQjlBytes, pn + 16);
                 }
             }
-            process_key_block<QJL, false, ONECOL>(kb, st, qB, sg, post0, post1, lut_lane, 16, kr);
-            process_key_block<QJL, false, ONECOL>(kc, st, qB, sg, post0, post1, lut_lane, 16, kr);
+            process_key_block<QJL, false, ONECOL, VPAIR>(kb, st, qB, sg, post0, post1, lut_lane, 16, kr);
+            process_key_block<QJL, false, ONECOL, VPAIR>(kc, st, qB, sg, post0, post1, lut_lane, 16, kr);
             // every lane has consumed its bytes of the stage: it can be refilled
             ring_consumed(ring);
             __syncwarp();
@@ -685,8 +700,10 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         }
         for (int k0 = nstage * kStageKeys; alive && k0 < nkeys; k0 += 16) {     // blocks with plain clamped loads
             const int nvalid = nkeys - k0 < 16 ? nkeys - k0 : 16;
-            load_tail_block<QJL>(kb, a, row0 + k0, nvalid, kr, va, vb, g, t);
-            process_key_block<QJL, true, ONECOL>(kb, st, qB, sg, post0, post1, lut_lane, nvalid, kr);
+            // groups of eight keys that lie completely below the user's length are stored pair-wise
+            const int64_t paired_left = (len & ~(int64_t)7) - (s0 + k0);
+            load_tail_block<QJL, VPAIR>(kb, a, row0 + k0, nvalid, paired_left >= 16 ? 16 : (paired_left >= 8 ? 8 : 0), kr, va, vb, g, t);
+            process_key_block<QJL, true, ONECOL, VPAIR>(kb, st, qB, sg, post0, post1, lut_lane, nvalid, kr);
         }
 
         // ---- epilogue ----------------------------------------------------------------------
@@ -903,8 +920,11 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
         if (rc != OMNI_OK) return rc;
     }
     const bool one_col = (a.Hq / a.Hkv) * a.T == 1;
-    auto kern = a.with_qjl ? (one_col ? qattn_mma_kernel<DT, true, true> : qattn_mma_kernel<DT, true, false>)
-                           : (one_col ? qattn_mma_kernel<DT, false, true> : qattn_mma_kernel<DT, false, false>);
+    auto kern = a.v_paired
+        ? (a.with_qjl ? (one_col ? qattn_mma_kernel<DT, true, true, true> : qattn_mma_kernel<DT, true, false, true>)
+                      : (one_col ? qattn_mma_kernel<DT, false, true, true> : qattn_mma_kernel<DT, false, false, true>))
+        : (a.with_qjl ? (one_col ? qattn_mma_kernel<DT, true, true, false> : qattn_mma_kernel<DT, true, false, false>)
+                      : (one_col ? qattn_mma_kernel<DT, false, true, false> : qattn_mma_kernel<DT, false, false, false>));
     rc = allow_full_smem(reinterpret_cast<const void*>(kern), dev);
     if (rc != OMNI_OK) return rc;
     kern<<<grid, kMmaWarps * 32, kMmaSmemBytes, st>>>(a, items, map_k, map_v);

@@ -155,7 +155,7 @@ const DeviceTables* tables_for_current_device() {
 
 using namespace omni;
 
-extern "C" int32_t omni_abi_version(void) { return 2; }
+extern "C" int32_t omni_abi_version(void) { return 3; }
 
 extern "C" const char* omni_last_error(void) { return g_last_error.c_str(); }
 

@@ -128,8 +128,10 @@ def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int, ragged: bool = False
 
 
 def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
-           seq_lens=None, cache_slots=None, rotate_q=False, unrotate_out=False, n_splits=None, lora=None):
-    """One call of ``omni_qattn_decode_lora``; ``lora`` = (x, lora_a, lora_b, lora_indices, lora_alpha) or None."""
+           seq_lens=None, cache_slots=None, rotate_q=False, unrotate_out=False, n_splits=None, lora=None,
+           v_paired=False):
+    """One call of ``omni_qattn_decode_lora``; ``lora`` = (x, lora_a, lora_b, lora_indices, lora_alpha) or None.
+    ``v_paired``: the V nibble rows are in the pair layout of :func:`pair_v_rows` (a resident cache's own format)."""
     dev = _lib.require_cuda(q, k_nibbles, k_qjl, k_norms, v_nibbles)
     lib = _lib.ensure_init(dev)
     B, Hq, T, D = q.shape
@@ -168,7 +170,7 @@ def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, w
             _lib.ptr(q), _lib.DTYPE_CODE[q.dtype], _lib.ptr(k_nibbles), _lib.ptr(k_qjl), _lib.ptr(k_norms),
             _lib.ptr(v_nibbles), _lib.ptr(cb), per_head, _lib.ptr(ids), uid, _lib.ptr(lens), _lib.ptr(slots),
             B, Hq, Hkv, T, S, Hkv * S, S, float(scale), int(bool(with_qjl)), int(bool(rotate_q)),
-            int(bool(unrotate_out)), int(n_splits), _lib.ptr(ws), ws_bytes, _lib.ptr(out), _lib.ptr(_lib.status_word(dev)),
+            int(bool(unrotate_out)), int(bool(v_paired)), int(n_splits), _lib.ptr(ws), ws_bytes, _lib.ptr(out), _lib.ptr(_lib.status_word(dev)),
             stream, lora_arg))
     return out
 
@@ -196,9 +198,10 @@ class OmniAttention(torch.autograd.Function):
 def omni_attn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id=0, scale: Optional[float] = None,
               with_qjl: bool = True, g_matrix=None, x=None, lora_a=None, lora_b=None, lora_indices=None,
               lora_alpha: float = 1.0, *, seq_lens=None, cache_slots=None, rotate_q: bool = False,
-              unrotate_out: bool = False, n_splits: Optional[int] = None) -> torch.Tensor:
+              unrotate_out: bool = False, n_splits: Optional[int] = None, v_paired: bool = False) -> torch.Tensor:
     """Fused INT4 + QJL attention with the optional per-user LoRA query update."""
-    plain = seq_lens is None and cache_slots is None and not rotate_q and not unrotate_out and n_splits is None
+    plain = (seq_lens is None and cache_slots is None and not rotate_q and not unrotate_out and n_splits is None
+             and not v_paired)
     if plain and torch.is_grad_enabled() and q.requires_grad:          # only then does the autograd node matter
         return OmniAttention.apply(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
                                    g_matrix, x, lora_a, lora_b, lora_indices, lora_alpha)
@@ -206,4 +209,28 @@ def omni_attn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id=0, sca
         scale = 1.0 / math.sqrt(HEAD_DIM)
     lora = None if x is None else (x, lora_a, lora_b, lora_indices, lora_alpha)
     return _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
-                  seq_lens, cache_slots, rotate_q, unrotate_out, n_splits, lora)
+                  seq_lens, cache_slots, rotate_q, unrotate_out, n_splits, lora, v_paired)
+
+
+def pair_v_rows(v_nibbles: torch.Tensor, lens_before=0, lens_after=None) -> None:
+    """Convert, in place, the V nibble rows ``(n_users, n_kv_heads, S, 64)`` of a resident cache to the pair layout
+    the tensor-core kernel reads without a shift-and-merge per lookup (``omni_v_pair_groups``): the groups of eight
+    keys that became complete when the users' lengths grew from ``lens_before`` to ``lens_after`` (ints, or int64
+    tensors of shape (n_users,); ``lens_after=None`` means the full capacity S).  Applying it again to the same
+    groups restores the reference layout."""
+    dev = _lib.require_cuda(v_nibbles)
+    lib = _lib.ensure_init(dev)
+    if not v_nibbles.is_contiguous():
+        raise ValueError("the cache's nibble array must be contiguous")
+    B, H, S, _ = v_nibbles.shape
+    if lens_after is None:
+        lens_after = S
+    tensors = isinstance(lens_before, torch.Tensor) or isinstance(lens_after, torch.Tensor)
+    if tensors:
+        before = torch.as_tensor(lens_before, device=dev).to(torch.int64).expand(B).contiguous()
+        after = torch.as_tensor(lens_after, device=dev).to(torch.int64).expand(B).contiguous()
+        args = (_lib.ptr(before), 0, _lib.ptr(after), 0)
+    else:
+        args = (None, int(lens_before), None, int(lens_after))
+    with _lib.on_device(dev):
+        _lib.check(lib.omni_v_pair_groups(_lib.ptr(v_nibbles), B, H, S, H * S, S, *args, _lib.stream_ptr(dev)))

@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 from .kernels.quantize import _NBYTES_NIBBLE, _NBYTES_QJL, _prep_codebooks, rotate_quantize_append
-from .kernels.fused_attention import _qattn, _auto_splits
+from .kernels.fused_attention import _qattn, _auto_splits, pair_v_rows
 
 HEAD_DIM = 128
 
@@ -118,7 +118,8 @@ class QuantizedKVCache:
     """
 
     def __init__(self, n_users: int, n_kv_heads: int, max_len: int, codebooks: torch.Tensor,
-                 device, user_ids: Optional[torch.Tensor] = None, store_v_residual: bool = True):
+                 device, user_ids: Optional[torch.Tensor] = None, store_v_residual: bool = True,
+                 pair_v: bool = False):
         self.device = torch.device(device)
         self.n_users, self.n_kv_heads, self.max_len = n_users, n_kv_heads, max_len
         self.codebooks = codebooks.to(device=self.device, dtype=torch.float32).contiguous()
@@ -130,6 +131,9 @@ class QuantizedKVCache:
             self.v_qjl, self.v_norms = mk(*shape, _NBYTES_QJL), mk(*shape, dt=torch.float32)
         else:   # attention never reads V's sign bits or norms: they are neither stored nor computed
             self.v_qjl = self.v_norms = None
+        # pair_v: V nibble rows are kept in the pair layout the tensor-core kernel reads fastest; every append
+        # converts the groups of eight keys it completes (``v_nib`` is then not interchangeable with the reference's)
+        self.pair_v = bool(pair_v)
         self.lens = torch.zeros(n_users, dtype=torch.int64, device=self.device)
         self.user_ids = (torch.arange(n_users, dtype=torch.int32, device=self.device) if user_ids is None
                          else user_ids.to(device=self.device, dtype=torch.int32).contiguous())
@@ -147,6 +151,8 @@ class QuantizedKVCache:
                                self.user_ids, rotate=rotate)
         rotate_quantize_append(v_new, self.v_nib, self.v_qjl, self.v_norms, self.lens, self.codebooks,
                                self.user_ids, rotate=rotate)
+        if self.pair_v:
+            pair_v_rows(self.v_nib, self.lens, self.lens + T)
         self.lens += T
 
     def attend(self, q: torch.Tensor, scale: Optional[float] = None, with_qjl: bool = True,
@@ -155,7 +161,8 @@ class QuantizedKVCache:
         if scale is None:
             scale = 1.0 / math.sqrt(HEAD_DIM)
         return _qattn(q, self.k_nib, self.k_qjl, self.k_norms, self.v_nib, self.codebooks, self.user_ids, scale,
-                      with_qjl, seq_lens=self.lens, rotate_q=rotate_q, unrotate_out=unrotate_out, n_splits=n_splits)
+                      with_qjl, seq_lens=self.lens, rotate_q=rotate_q, unrotate_out=unrotate_out, n_splits=n_splits,
+                      v_paired=self.pair_v)
 
 
 class HostDecodeStep:
@@ -167,7 +174,7 @@ class HostDecodeStep:
 
     def __init__(self, k_nib, k_qjl, k_norms, v_nib, codebooks, n_heads: int, batch: int, q_dtype=torch.bfloat16,
                  user_id=0, seq_lens=None, cache_slots=None, scale: Optional[float] = None, with_qjl: bool = True,
-                 T: int = 1, n_chunks: Optional[int] = None, n_splits: Optional[int] = None):
+                 T: int = 1, n_chunks: Optional[int] = None, n_splits: Optional[int] = None, v_paired: bool = False):
         self.dev = _lib.require_cuda(k_nib, k_qjl, k_norms, v_nib)
         self.lib = _lib.ensure_init(self.dev)
         self.k_nib, self.k_qjl, self.k_norms, self.v_nib = k_nib, k_qjl, k_norms, v_nib
@@ -185,7 +192,7 @@ class HostDecodeStep:
         self.scale = float(scale if scale is not None else 1.0 / math.sqrt(HEAD_DIM))
         if n_chunks is None:                       # chunks of at least ~2k users keep every SM busy
             n_chunks = max(1, min(8, batch // 2048))
-        self.with_qjl, self.n_chunks = int(bool(with_qjl)), int(n_chunks)
+        self.with_qjl, self.n_chunks, self.v_paired = int(bool(with_qjl)), int(n_chunks), int(bool(v_paired))
         per_chunk = -(-batch // self.n_chunks)
         self.n_splits = int(n_splits) if n_splits is not None else _auto_splits(per_chunk, n_heads, self.Hkv, T, self.S, seq_lens is not None)
         self.ws_bytes = 2 * self.lib.omni_qattn_workspace_bytes(per_chunk, n_heads, T, self.n_splits)
@@ -210,6 +217,6 @@ class HostDecodeStep:
                 _lib.ptr(self.k_nib), _lib.ptr(self.k_qjl), _lib.ptr(self.k_norms), _lib.ptr(self.v_nib),
                 _lib.ptr(self.cb), self.per_head, _lib.ptr(self.ids), self.uid, _lib.ptr(self.lens), _lib.ptr(self.slots),
                 self.B, self.Hq, self.Hkv, self.T, self.S, self.Hkv * self.S, self.S, self.scale, self.with_qjl,
-                _lib.ptr(self.out_stage), _lib.ptr(self.out_host), self.n_chunks,
+                self.v_paired, _lib.ptr(self.out_stage), _lib.ptr(self.out_host), self.n_chunks,
                 self.n_splits, _lib.ptr(self.ws), self.ws_bytes, _lib.ptr(_lib.status_word(self.dev))))
         return self.out_host

@@ -34,7 +34,7 @@ def test_header_symbols_exported(lib):
 
 
 def test_abi_version_and_error_string(lib):
-    assert lib.omni_abi_version() == 2
+    assert lib.omni_abi_version() == 3
     assert lib.omni_gtable_host(None, 0, 1) == _lib.ERR_ARG
     assert b"NULL" in lib.omni_last_error()
     buf = np.empty((1, 64, 4), dtype=np.uint32)

@@ -361,3 +361,51 @@ def test_bounded_wait_runs_out_and_is_reported(dev):
     q = torch.randn(1, 1, 1, 128, generator=gen).to(torch.bfloat16)
     out = fa.omni_attn(*to_dev(dev, q, kn, kq, kr, vn, cb), user_id=0)       # the device still works
     assert (out.cpu() - orc.decode_attention(q, kn, kq, kr, vn, cb, 0)).abs().max() <= ATOL
+
+
+@pytest.mark.parametrize("S", [1, 7, 8, 9, 15, 16, 17, 31, 33, 64, 100, 129, 300, 777])
+def test_pair_layout_of_v_gives_identical_results(dev, S):
+    """The pair layout of V (a resident cache's own format, ``pair_v_rows``) changes where nibbles sit, not what
+    is computed: the result equals the reference-layout call bit for bit, for every key count, with splits, with
+    ragged lengths and grouped queries, in both kernels; converting twice restores the reference bytes."""
+    fa = attn_mod()
+    kn, kq, kr, vn, cb, gen = make_cache(3, 2, S, seed=1000 + S, user_id=4)
+    q = torch.randn(3, 8, 1, 128, generator=gen).to(torch.bfloat16)
+    lens = torch.tensor([S, max(1, S // 2), max(1, S - 3)], dtype=torch.int64)
+    d = to_dev(dev, q, kn, kq, kr, vn, cb)
+    paired = d[4].clone()
+    fa.pair_v_rows(paired, 0, lens.to(dev))
+    if S >= 8:
+        assert not torch.equal(paired, d[4])
+    for ns in (1, 2):
+        ref = fa.omni_attn(*d, user_id=4, seq_lens=lens.to(dev), n_splits=ns)
+        got = fa.omni_attn(d[0], d[1], d[2], d[3], paired, d[5], user_id=4, seq_lens=lens.to(dev), n_splits=ns, v_paired=True)
+        assert torch.equal(got, ref), (S, ns)
+    for b in range(3):
+        n = int(lens[b])
+        want = orc.decode_attention(q[b:b + 1], kn[b:b + 1, :, :n], kq[b:b + 1, :, :n], kr[b:b + 1, :, :n], vn[b:b + 1, :, :n], cb, 4)
+        assert (got[b:b + 1].cpu() - want).abs().max() <= ATOL
+    fa.pair_v_rows(paired, 0, lens.to(dev))
+    assert torch.equal(paired, d[4])
+    full = d[4].clone()
+    fa.pair_v_rows(full)                                                  # scalar lengths: the whole capacity
+    whole = fa.omni_attn(d[0], d[1], d[2], d[3], full, d[5], user_id=4, v_paired=True)
+    assert torch.equal(whole, fa.omni_attn(*d, user_id=4))
+
+
+def test_cache_with_paired_v_follows_appends(dev):
+    """A serving cache that keeps V pair-wise converts the groups each append completes, whatever the chunk sizes."""
+    from omnistack_rs_b200.serving import QuantizedKVCache
+    gen = torch.Generator().manual_seed(77)
+    B, H = 3, 2
+    cb = torch.sort(torch.randn(H, 16, generator=gen), dim=1).values
+    plain = QuantizedKVCache(B, H, 80, cb, dev, store_v_residual=False)
+    fast = QuantizedKVCache(B, H, 80, cb, dev, store_v_residual=False, pair_v=True)
+    for n in (3, 5, 1, 8, 2, 13, 16, 7):
+        kc = torch.randn(B, H, n, 128, generator=gen).to(torch.bfloat16).to(dev)
+        vc = torch.randn(B, H, n, 128, generator=gen).to(torch.bfloat16).to(dev)
+        plain.append(kc, vc)
+        fast.append(kc, vc)
+        q = torch.randn(B, 4, 1, 128, generator=gen).to(torch.bfloat16).to(dev)
+        assert torch.equal(fast.attend(q), plain.attend(q)), n
+    assert not torch.equal(fast.v_nib, plain.v_nib)

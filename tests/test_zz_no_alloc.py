@@ -42,7 +42,7 @@ def _call(lib, name, q, kn, kq, kr, vn, cb, lens, n_splits, workspace=None):
     out = torch.full((B, Hq, T, 128), float("nan"), dtype=torch.float32, device=q.device)
     common = [_lib.ptr(q), _lib.DTYPE_CODE[q.dtype], _lib.ptr(kn), _lib.ptr(kq), _lib.ptr(kr), _lib.ptr(vn),
               _lib.ptr(cb), 1, None, 6, _lib.ptr(lens), None, B, Hq, Hkv, T, S, Hkv * S, S,
-              1.0 / math.sqrt(128), 1, 0, 0, n_splits]
+              1.0 / math.sqrt(128), 1, 0, 0, 0, n_splits]
     stream = _lib.stream_ptr(q.device)
     if name == "noalloc":
         status = lib.omni_qattn_decode_noalloc(*common, _lib.ptr(out), stream)
@@ -105,7 +105,7 @@ def test_noalloc_entry_refuses_oversized_request():
     with torch.cuda.device(dev):
         status = lib.omni_qattn_decode_noalloc(
             _lib.ptr(d[0]), 1, _lib.ptr(d[1]), _lib.ptr(d[2]), _lib.ptr(d[3]), _lib.ptr(d[4]), _lib.ptr(d[5]), 1,
-            None, 6, None, None, too_many, 1, 1, 1, 64, 64, 64, 0.1, 1, 0, 0, 2, _lib.ptr(out), None)
+            None, 6, None, None, too_many, 1, 1, 1, 64, 64, 64, 0.1, 1, 0, 0, 0, 2, _lib.ptr(out), None)
     assert status == _lib.ERR_UNSUPPORTED
     msg = lib.omni_last_error().decode()
     assert "scratch" in msg and "n_splits" in msg
@@ -134,7 +134,7 @@ side = torch.cuda.Stream(device=dev)                # a non-blocking stream: no 
 with torch.cuda.device(dev), torch.cuda.stream(side):
     st = lib.omni_qattn_decode_noalloc(
         _lib.ptr(d[0]), 1, _lib.ptr(d[1]), _lib.ptr(d[2]), _lib.ptr(d[3]), _lib.ptr(d[4]), _lib.ptr(d[5]), 1,
-        None, 6, None, None, B, Hq, Hkv, 1, S, Hkv * S, S, 1.0 / math.sqrt(128), 1, 0, 0, n_splits,
+        None, 6, None, None, B, Hq, Hkv, 1, S, Hkv * S, S, 1.0 / math.sqrt(128), 1, 0, 0, 0, n_splits,
         _lib.ptr(out), side.cuda_stream)
 side.synchronize()
 assert st == _lib.OK, lib.omni_last_error()
