@@ -305,6 +305,12 @@ __global__ void __launch_bounds__(256) v_pair_groups_kernel(uint8_t* v_nib, int6
 
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// the part of a split-K workspace no call can do without: partial states and the ticket counters behind them
+static size_t partials_and_counter_bytes(int64_t B, int32_t Hq, int32_t T, int32_t n_splits) {
+    if (n_splits <= 1 || B <= 0 || Hq <= 0 || T <= 0) return 0;
+    return (size_t)B * Hq * T * n_splits * kWsStride * sizeof(float) + kWorkCounterBytes;
+}
+
 static int32_t validate(const AttnArgs& a, size_t ws_bytes) {
     OMNI_REQUIRE(a.B >= 0 && a.Hq > 0 && a.Hkv > 0 && a.T >= 0 && a.S >= 0, OMNI_ERR_ARG, "qattn: bad extent");
     OMNI_REQUIRE(a.Hq % a.Hkv == 0, OMNI_ERR_ARG, "qattn: Hq=%d is not a multiple of Hkv=%d", a.Hq, a.Hkv);
@@ -318,7 +324,7 @@ static int32_t validate(const AttnArgs& a, size_t ws_bytes) {
     OMNI_REQUIRE(aligned(a.k_nib, 16) && aligned(a.v_nib, 16) && aligned(a.k_qjl, 8) && aligned(a.k_norms, 4),
                  OMNI_ERR_ARG, "qattn: cache arrays must be 16-byte (nibbles) / 8-byte (sign bytes) aligned");
     if (a.n_splits > 1) {
-        const size_t need = omni_qattn_workspace_bytes(a.B, a.Hq, a.T, a.n_splits);
+        const size_t need = partials_and_counter_bytes(a.B, a.Hq, a.T, a.n_splits);
         OMNI_REQUIRE(a.ws && aligned(a.ws, 16) && ws_bytes >= need, OMNI_ERR_ARG,
                      "qattn: workspace of %zu bytes needed for %d splits, got %zu", need, a.n_splits, ws_bytes);
     }
@@ -336,7 +342,7 @@ static KernelChoice kernel_choice_from_env() {
     return kAuto;
 }
 
-static int32_t launch(const AttnArgs& a, cudaStream_t st) {
+static int32_t launch(const AttnArgs& a, cudaStream_t st, size_t ws_bytes) {
     if (a.B == 0 || a.T == 0) return OMNI_OK;
     const KernelChoice choice = kernel_choice_from_env();
     // measured crossover: the tensor-core kernel wins from 128 keys on, and for shorter caches once the
@@ -345,8 +351,18 @@ static int32_t launch(const AttnArgs& a, cudaStream_t st) {
                          (choice == kMma || (choice == kAuto && (a.S >= 128 || a.B * a.Hq * a.T >= 1024)));
     if (use_mma) {
         AttnArgs m = a;
-        if (a.n_splits > 1)      // the ticket counters sit behind the partial states (omni_qattn_workspace_bytes)
-            m.work_counter = reinterpret_cast<uint32_t*>(a.ws + (size_t)a.B * a.Hq * a.T * a.n_splits * kWsStride);
+        if (a.n_splits > 1) {    // the ticket counters sit behind the partial states, the prepared query operands behind those
+            const size_t partial_floats = (size_t)a.B * a.Hq * a.T * a.n_splits * kWsStride;
+            m.work_counter = reinterpret_cast<uint32_t*>(a.ws + partial_floats);
+            // OMNI_QATTN_PREP=0 keeps every work item building its own operands (tests and profiling)
+            const char* prep_env = getenv("OMNI_QATTN_PREP");
+            // Preparing the operands in a launch of its own pays once warps serve several items each (throughput);
+            // a call whose items all run at once would only see the extra launch on its critical path (latency).
+            const int64_t n_items = a.B * a.Hkv * (((int64_t)(a.Hq / a.Hkv) * a.T + 7) / 8) * a.n_splits;
+            const bool many = n_items >= 2 * 148 * 12 || (prep_env && prep_env[0] == '1');
+            if (many && !(prep_env && prep_env[0] == '0') && ws_bytes >= omni_qattn_workspace_bytes(a.B, a.Hq, a.T, a.n_splits))
+                m.qprep = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(a.ws + partial_floats) + kWorkCounterBytes);
+        }
         const int32_t rc = launch_mma(m, st);
         if (rc != OMNI_OK) return rc;
     }
@@ -430,7 +446,9 @@ using namespace omni;
 
 extern "C" size_t omni_qattn_workspace_bytes(int64_t B, int32_t Hq, int32_t T, int32_t n_splits) {
     if (n_splits <= 1 || B <= 0 || Hq <= 0 || T <= 0) return 0;
-    return (size_t)B * Hq * T * n_splits * kWsStride * sizeof(float) + kWorkCounterBytes;
+    // partial states, ticket counters, and room for the prepared query operands of every (user, kv head, tile of 8
+    // query columns): at most Hq * ceil((T + 7) / 8) such tiles per user whatever the head grouping
+    return partials_and_counter_bytes(B, Hq, T, n_splits) + (size_t)B * Hq * ((T + 7 + 7) / 8) * kPrepBytesPerUnit;
 }
 
 extern "C" int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
@@ -450,7 +468,7 @@ extern "C" int32_t omni_qattn_decode(const void* q, int32_t q_dtype,
                (float*)workspace, out, tb->rows, status_word, nullptr, v_paired};
     int32_t st = validate(a, workspace_bytes);
     if (st != OMNI_OK) return st;
-    return launch(a, (cudaStream_t)stream);
+    return launch(a, (cudaStream_t)stream, workspace_bytes);
 }
 
 static size_t lora_q_bytes(int64_t B, int32_t Hq, int32_t T) {
@@ -492,7 +510,7 @@ extern "C" int32_t omni_qattn_decode_lora(const void* q, int32_t q_dtype,
     st = omni_lora_q(q, q_dtype, lora->x, lora->lora_a, lora->lora_b, lora->lora_indices, lora->n_adapters, lora->alpha,
                      B, Hq, T, lora->hidden, lora->rank, q_eff, status_word, stream);
     if (st != OMNI_OK) return st;
-    return launch(a, (cudaStream_t)stream);
+    return launch(a, (cudaStream_t)stream, workspace_bytes - (B == 0 || T == 0 ? 0 : qb));
 }
 
 extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, void* q_stage,
@@ -545,7 +563,7 @@ extern "C" int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, v
                    n_splits > 1 ? reinterpret_cast<float*>((char*)workspace + (size_t)(c & 1) * ws_chunk) : nullptr,
                    out_stage + qoff, tb->rows, status_word, nullptr, v_paired};
         int32_t stc = validate(a, ws_chunk);
-        if (stc == OMNI_OK) stc = launch(a, st);
+        if (stc == OMNI_OK) stc = launch(a, st, ws_chunk);
         if (stc != OMNI_OK) { cudaStreamSynchronize(g_hs[dev].s[0]); cudaStreamSynchronize(g_hs[dev].s[1]); return stc; }
         OMNI_CUDA(cudaMemcpyAsync(out_host + qoff, out_stage + qoff, (size_t)nb * Hq * T * kHeadDim * sizeof(float),
                                   cudaMemcpyDeviceToHost, st));
@@ -586,7 +604,9 @@ extern "C" int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
                                              int64_t ks_b, int64_t ks_h, float scale, int32_t with_qjl,
                                              int32_t rotate_q, int32_t unrotate_out, int32_t v_paired, int32_t n_splits,
                                              float* out, void* stream) {
-    const size_t need = omni_qattn_workspace_bytes(B, Hq, T, n_splits);
+    // partial states and ticket counters only: the built-in scratch leaves out the prepared query operands that a
+    // caller-provided workspace has room for (every work item builds its own here)
+    const size_t need = partials_and_counter_bytes(B, Hq, T, n_splits);
     OMNI_REQUIRE(need <= kStaticScratchBytes, OMNI_ERR_UNSUPPORTED,
                  "omni_qattn_decode_noalloc: B*Hq*T*n_splits = %lld partial states need %zu bytes of scratch but the "
                  "built-in array holds %zu; lower n_splits or use omni_qattn_decode with a caller-provided workspace",
@@ -599,7 +619,7 @@ extern "C" int32_t omni_qattn_decode_noalloc(const void* q, int32_t q_dtype,
                arr.scratch, out, arr.rows, arr.status, nullptr, v_paired};
     st = validate(a, kStaticScratchBytes);
     if (st != OMNI_OK) return st;
-    return launch(a, (cudaStream_t)stream);
+    return launch(a, (cudaStream_t)stream, need);
 }
 
 extern "C" int32_t omni_qattn_noalloc_status(int32_t* value_out, int32_t clear) {

@@ -19,6 +19,9 @@ struct AttnArgs {
     int v_paired;              // V nibble rows are stored pair-wise (see omni_v_pair_groups): within every group of eight
                                // keys that lies completely below the user's length, the rows of keys (0,3), (1,2), (4,7),
                                // (5,6) hold the even-d / odd-d nibbles of both keys instead of one key's 128 nibbles each
+    uint32_t* qprep;           // tensor-core kernel, split-K calls: device scratch for the prepared query operands of every
+                               // (user, kv head, tile of 8 query columns), kPrepBytesPerUnit each (null: every work item
+                               // builds its own)
     int only_if_wide;          // lane-per-key kernel: 1 = run only when the codebooks are outside the fp16 table's
                                // range (it then completes a call whose tensor-core launch stood down), 0 = always
 };
@@ -34,6 +37,7 @@ __device__ __forceinline__ bool centroid_is_wide(float c) { return !(fabsf(c) < 
 
 constexpr int kWsStride = 132;     // floats per split-K partial: 128 accumulators, max, sum, 2 pad
 constexpr size_t kWorkCounterBytes = 4096;   // kSeeds (the most kv heads a call may have) 32-bit counters
+constexpr size_t kPrepBytesPerUnit = 28 * 4 * 32;   // prepared query operands of one work item: 28 words per lane
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

@@ -370,6 +370,200 @@ __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState&
 }
 
 
+// The B operands of one work item -- the scaled query columns as fp16 pairs, the q.g projections quantised to int8
+// with their seeds and steps, the per-column power-of-two post-scales -- as the registers of the main loop.
+struct QueryOperands {
+    uint32_t qB[8][2];
+    SignB sg;
+    float post0, post1;
+};
+constexpr int kPrepWords = 28;              // 16 + 4 + 2 + 2 + 2 words per lane, padded to seven 16-byte vectors
+static_assert(kPrepBytesPerUnit == kPrepWords * 4 * 32, "prepared operands: size used by the workspace layout");
+
+// Builds them from the query rows of (user b, kv head hkv, columns col0 .. col0 + ncols).  `qrow` is this warp's
+// shared scratch (8 x 128 fp32 query rows, reused for the q.g projections) and `colinfo` the per-column scalars
+// behind it.  Every lane of the warp must call.
+template <int DT, bool QJL>
+__device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t b, int hkv, int col0, int ncols, int Gq, float qs,
+                                                     float* qrow, float4* colinfo, int lane, QueryOperands& qo) {
+    const int g = lane >> 2, t = lane & 3;
+    float* qg_s = qrow;
+    uint32_t (&qB)[8][2] = qo.qB;
+    SignB& sg = qo.sg;
+    // ---- prologue: B operands (scaled queries, q.g projections) --------------------------------
+    // 1. every column's query row goes to shared memory in fp32 together with its scalars
+    for (int c = 0; c < ncols; ++c) {
+        const int cg = col0 + c;
+        const int64_t qrow_idx = (b * a.Hq + (int64_t)hkv * Gq + cg / a.T) * a.T + (cg % a.T);
+        float qv[4];
+        Elem<DT>::load4(a.q, qrow_idx * kHeadDim + 4 * lane, qv);
+        if (a.rotate_q) wht128_warp(qv, lane);                  // the rotation folded into the query (fp32, not rounded)
+        const float amax = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3]))));
+        // fp16 operands stay below 2^10 in magnitude; the power of two is re-applied to the scores
+        const float mx = amax * fabsf(qs);
+        float post = 1.f;
+        if (mx > 1024.f) post = exp2f(ceilf(log2f(mx * (1.f / 1024.f))));
+        const float f = qs / post;
+        // int16 fixed point for the q.g projections: amax * sq in [2^14 - 32, 2^15 - 64)
+        const int E = (__float_as_uint(amax) >> 23) & 0xFF;
+        const float sq = (E < 16 || E == 255) ? 0.f : __uint_as_float(((uint32_t)(267 - E) << 23) | 0x7F8000u);
+        *reinterpret_cast<float4*>(qrow + c * 128 + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
+        if (lane == 0) colinfo[c] = make_float4(f, post, sq > 0.f ? kQjlCoef * f / sq : 0.f, sq);
+    }
+    __syncwarp();
+    // 2. thread (g, t) owns column g: its 32 dims d = 32t .. 32t+31 as fp16 (scores) and as int8 limbs (q.g)
+    uint32_t bh[4][2], bl[4][2];
+    if (g < ncols) {
+        const float4 ci = colinfo[g];
+        float qd[32];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float4 v = *reinterpret_cast<const float4*>(qrow + g * 128 + 32 * t + 4 * k);
+            qd[4 * k] = v.x; qd[4 * k + 1] = v.y; qd[4 * k + 2] = v.z; qd[4 * k + 3] = v.w;
+            qB[k][0] = pack_half2(v.x * ci.x, v.y * ci.x);
+            qB[k][1] = pack_half2(v.z * ci.x, v.w * ci.x);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(fmaf(qd[8 * ks + k], ci.w, 12582912.f));   // low 16 bits = int16
+            const uint32_t p01 = __byte_perm(v[0], v[1], 0x5140), p23 = __byte_perm(v[2], v[3], 0x5140);
+            const uint32_t p45 = __byte_perm(v[4], v[5], 0x5140), p67 = __byte_perm(v[6], v[7], 0x5140);
+            bl[ks][0] = __byte_perm(p01, p23, 0x5410); bh[ks][0] = __byte_perm(p01, p23, 0x7632);
+            bl[ks][1] = __byte_perm(p45, p67, 0x5410); bh[ks][1] = __byte_perm(p45, p67, 0x7632);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { qB[k][0] = 0u; qB[k][1] = 0u; }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) { bl[ks][0] = 0u; bl[ks][1] = 0u; bh[ks][0] = 0u; bh[ks][1] = 0u; }
+    }
+    float post0 = 1.f, post1 = 1.f;
+    if (2 * t < ncols) post0 = colinfo[2 * t].y;
+    if (2 * t + 1 < ncols) post1 = colinfo[2 * t + 1].y;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { sg.z[k] = 0u; sg.zq[k] = 0; }
+    sg.cs0 = 0.f; sg.cs1 = 0.f;
+    if (QJL) {
+        // 3. q.g for all columns on the int8 tensor cores: A = G (+-1, built from the bit rows), B = the limbs;
+        //    MMA k index 4t'+j / 16+4t'+j  <->  d = 32t' + 8ks + j / + 4 + j
+        const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
+        const uint32_t* grow = a.g_rows + (size_t)seed_of(uid, hkv) * kQjlDim * 4;
+        const float inv0 = (2 * t < ncols) ? colinfo[2 * t].z : 0.f, inv1 = (2 * t + 1 < ncols) ? colinfo[2 * t + 1].z : 0.f;
+        __syncwarp();                                            // all reads of the query rows are done
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            const uint32_t w0 = __ldg(grow + (16 * mt + g) * 4 + t), w1 = __ldg(grow + (16 * mt + g + 8) * 4 + t);
+            int chi[4] = {0, 0, 0, 0}, clo[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint32_t x0 = w0 >> (8 * ks), x1 = w1 >> (8 * ks);
+                const uint32_t a0 = pm1_bytes<0>(x0), a1 = pm1_bytes<0>(x1), a2 = pm1_bytes<4>(x0), a3 = pm1_bytes<4>(x1);
+                imma_acc_s8s8(chi, a0, a1, a2, a3, bh[ks][0], bh[ks][1]);
+                imma_acc_s8u8(clo, a0, a1, a2, a3, bl[ks][0], bl[ks][1]);
+            }
+            // C element j: projection 16mt + g + 8(j>>1), column 2t + (j&1)
+            if (2 * t < ncols) {
+                qg_s[(2 * t) * 64 + 16 * mt + g] = (float)(chi[0] * 256 + clo[0]) * inv0;
+                qg_s[(2 * t) * 64 + 16 * mt + g + 8] = (float)(chi[2] * 256 + clo[2]) * inv0;
+            }
+            if (2 * t + 1 < ncols) {
+                qg_s[(2 * t + 1) * 64 + 16 * mt + g] = (float)(chi[1] * 256 + clo[1]) * inv1;
+                qg_s[(2 * t + 1) * 64 + 16 * mt + g + 8] = (float)(chi[3] * 256 + clo[3]) * inv1;
+            }
+        }
+        __syncwarp();
+        // 4. quantise column g's 64 projections to int8 with one step; keep their sum even (it is halved)
+        //    (every lane runs the shuffles; lanes of unused columns work on zeros)
+        const bool mine = g < ncols;
+        float v[16];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (mine) x = *reinterpret_cast<const float4*>(qg_s + g * 64 + 16 * t + 4 * k);
+            v[4 * k] = x.x; v[4 * k + 1] = x.y; v[4 * k + 2] = x.z; v[4 * k + 3] = x.w;
+        }
+        float am = 0.f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) am = fmaxf(am, fabsf(v[k]));
+        am = fmaxf(am, __shfl_xor_sync(kFullMask, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(kFullMask, am, 2));
+        const float step = am > 0.f ? am * (1.f / 127.f) : 1.f, rstep = 1.f / step;
+        int z[16], zsum = 0;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) { z[k] = __float2int_rn(v[k] * rstep); zsum += z[k]; }
+        zsum += __shfl_xor_sync(kFullMask, zsum, 1);
+        zsum += __shfl_xor_sync(kFullMask, zsum, 2);
+        const int z_first = __shfl_sync(kFullMask, z[0], lane & ~3);     // the column's first projection (lane t = 0)
+        if (zsum & 1) {                                                  // uniform over the column's four lanes
+            const int fix = z_first < 127 ? 1 : -1;
+            if (t == 0) z[0] += fix;
+            zsum += fix;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t p01 = __byte_perm(z[4 * k], z[4 * k + 1], 0x5140), p23 = __byte_perm(z[4 * k + 2], z[4 * k + 3], 0x5140);
+            sg.z[k] = __byte_perm(p01, p23, 0x5410);
+        }
+        const float mycs = mine ? -2.f * step : 0.f;
+        const int myzh = zsum / 2;
+        // the thread's score columns are 2t and 2t+1: fetch their seeds and steps from those columns' lanes
+        sg.zq[0] = sg.zq[2] = __shfl_sync(kFullMask, myzh, 8 * t);
+        sg.zq[1] = sg.zq[3] = __shfl_sync(kFullMask, myzh, 8 * t + 4);
+        sg.cs0 = __shfl_sync(kFullMask, mycs, 8 * t);
+        sg.cs1 = __shfl_sync(kFullMask, mycs, 8 * t + 4);
+    }
+    __syncwarp();
+
+    qo.post0 = post0; qo.post1 = post1;
+}
+
+__device__ __forceinline__ void pack_query_operands(const QueryOperands& qo, uint4 (&v)[kPrepWords / 4]) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = make_uint4(qo.qB[2 * k][0], qo.qB[2 * k][1], qo.qB[2 * k + 1][0], qo.qB[2 * k + 1][1]);
+    v[4] = make_uint4(qo.sg.z[0], qo.sg.z[1], qo.sg.z[2], qo.sg.z[3]);
+    v[5] = make_uint4((uint32_t)qo.sg.zq[0], (uint32_t)qo.sg.zq[1], __float_as_uint(qo.sg.cs0), __float_as_uint(qo.sg.cs1));
+    v[6] = make_uint4(__float_as_uint(qo.post0), __float_as_uint(qo.post1), 0u, 0u);
+}
+__device__ __forceinline__ void unpack_query_operands(const uint4 (&v)[kPrepWords / 4], QueryOperands& qo) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        qo.qB[2 * k][0] = v[k].x; qo.qB[2 * k][1] = v[k].y; qo.qB[2 * k + 1][0] = v[k].z; qo.qB[2 * k + 1][1] = v[k].w;
+    }
+    qo.sg.z[0] = v[4].x; qo.sg.z[1] = v[4].y; qo.sg.z[2] = v[4].z; qo.sg.z[3] = v[4].w;
+    qo.sg.zq[0] = qo.sg.zq[2] = (int)v[5].x; qo.sg.zq[1] = qo.sg.zq[3] = (int)v[5].y;
+    qo.sg.cs0 = __uint_as_float(v[5].z); qo.sg.cs1 = __uint_as_float(v[5].w);
+    qo.post0 = __uint_as_float(v[6].x); qo.post1 = __uint_as_float(v[6].y);
+}
+
+// Preparation launch of split-K calls: one warp per (user, kv head, tile of 8 query columns) builds the item's
+// B operands once and stores them lane by lane; every split of the item then fetches seven 16-byte vectors per
+// lane instead of repeating the projections.
+template <int DT, bool QJL>
+__global__ void __launch_bounds__(128) qattn_prep_kernel(AttnArgs a, int64_t n_units) {
+    __shared__ __align__(16) unsigned char scratch[4][kWarpScratchBytes];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int Gq = a.Hq / a.Hkv, ncols_all = Gq * a.T, n_ctiles = (ncols_all + 7) / 8;
+    const float qs = a.scale * kLog2e;
+    float* qrow = reinterpret_cast<float*>(scratch[warp]);
+    float4* colinfo = reinterpret_cast<float4*>(qrow + 8 * 128);
+    for (int64_t unit = (int64_t)blockIdx.x * 4 + warp; unit < n_units; unit += (int64_t)gridDim.x * 4) {
+        const int col0 = 8 * (int)(unit % n_ctiles);
+        const int hkv = (int)((unit / n_ctiles) % a.Hkv);
+        const int64_t b = unit / n_ctiles / a.Hkv;
+        const int ncols = ncols_all - col0 < 8 ? ncols_all - col0 : 8;
+        QueryOperands qo;
+        build_query_operands<DT, QJL>(a, b, hkv, col0, ncols, Gq, qs, qrow, colinfo, lane, qo);
+        uint4 v[kPrepWords / 4];
+        pack_query_operands(qo, v);
+        uint4* dst = reinterpret_cast<uint4*>(a.qprep) + unit * (kPrepWords / 4) * 32 + lane;
+#pragma unroll
+        for (int k = 0; k < kPrepWords / 4; ++k) dst[32 * k] = v[k];
+        __syncwarp();
+    }
+}
+
 // Per-warp ring of TMA stages: each holds kStageKeys rows of K nibbles followed by as many of V.
 // The stage filled next and the stage consumed next advance round-robin; `*_phase` is the parity of
 // the mbarrier phase that the fill completes / the consumer waits for.
@@ -513,132 +707,22 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         }
 
         // ---- prologue: B operands (scaled queries, q.g projections) --------------------------------
-        // 1. every column's query row goes to shared memory in fp32 together with its scalars
-        for (int c = 0; c < ncols; ++c) {
-            const int cg = col0 + c;
-            const int64_t qrow_idx = (b * a.Hq + (int64_t)hkv * Gq + cg / a.T) * a.T + (cg % a.T);
-            float qv[4];
-            Elem<DT>::load4(a.q, qrow_idx * kHeadDim + 4 * lane, qv);
-            if (a.rotate_q) wht128_warp(qv, lane);                  // the rotation folded into the query (fp32, not rounded)
-            const float amax = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3]))));
-            // fp16 operands stay below 2^10 in magnitude; the power of two is re-applied to the scores
-            const float mx = amax * fabsf(qs);
-            float post = 1.f;
-            if (mx > 1024.f) post = exp2f(ceilf(log2f(mx * (1.f / 1024.f))));
-            const float f = qs / post;
-            // int16 fixed point for the q.g projections: amax * sq in [2^14 - 32, 2^15 - 64)
-            const int E = (__float_as_uint(amax) >> 23) & 0xFF;
-            const float sq = (E < 16 || E == 255) ? 0.f : __uint_as_float(((uint32_t)(267 - E) << 23) | 0x7F8000u);
-            *reinterpret_cast<float4*>(qrow + c * 128 + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
-            if (lane == 0) colinfo[c] = make_float4(f, post, sq > 0.f ? kQjlCoef * f / sq : 0.f, sq);
-        }
-        __syncwarp();
-        // 2. thread (g, t) owns column g: its 32 dims d = 32t .. 32t+31 as fp16 (scores) and as int8 limbs (q.g)
-        uint32_t qB[8][2];
-        SignB sg;
-        uint32_t bh[4][2], bl[4][2];
-        if (g < ncols) {
-            const float4 ci = colinfo[g];
-            float qd[32];
+        // computed here, or fetched when a preparation launch has stored them (split-K calls, whose items would
+        // otherwise repeat this work once per split)
+        QueryOperands qo;
+        if (a.qprep) {
+            const int64_t unit = (b * a.Hkv + hkv) * n_ctiles + col0 / 8;
+            const uint4* src = reinterpret_cast<const uint4*>(a.qprep) + unit * (kPrepWords / 4) * 32 + lane;
+            uint4 v[kPrepWords / 4];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float4 v = *reinterpret_cast<const float4*>(qrow + g * 128 + 32 * t + 4 * k);
-                qd[4 * k] = v.x; qd[4 * k + 1] = v.y; qd[4 * k + 2] = v.z; qd[4 * k + 3] = v.w;
-                qB[k][0] = pack_half2(v.x * ci.x, v.y * ci.x);
-                qB[k][1] = pack_half2(v.z * ci.x, v.w * ci.x);
-            }
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                uint32_t v[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(fmaf(qd[8 * ks + k], ci.w, 12582912.f));   // low 16 bits = int16
-                const uint32_t p01 = __byte_perm(v[0], v[1], 0x5140), p23 = __byte_perm(v[2], v[3], 0x5140);
-                const uint32_t p45 = __byte_perm(v[4], v[5], 0x5140), p67 = __byte_perm(v[6], v[7], 0x5140);
-                bl[ks][0] = __byte_perm(p01, p23, 0x5410); bh[ks][0] = __byte_perm(p01, p23, 0x7632);
-                bl[ks][1] = __byte_perm(p45, p67, 0x5410); bh[ks][1] = __byte_perm(p45, p67, 0x7632);
-            }
+            for (int k = 0; k < kPrepWords / 4; ++k) v[k] = __ldg(src + 32 * k);
+            unpack_query_operands(v, qo);
         } else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) { qB[k][0] = 0u; qB[k][1] = 0u; }
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) { bl[ks][0] = 0u; bl[ks][1] = 0u; bh[ks][0] = 0u; bh[ks][1] = 0u; }
+            build_query_operands<DT, QJL>(a, b, hkv, col0, ncols, Gq, qs, qrow, colinfo, lane, qo);
         }
-        float post0 = 1.f, post1 = 1.f;
-        if (2 * t < ncols) post0 = colinfo[2 * t].y;
-        if (2 * t + 1 < ncols) post1 = colinfo[2 * t + 1].y;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) { sg.z[k] = 0u; sg.zq[k] = 0; }
-        sg.cs0 = 0.f; sg.cs1 = 0.f;
-        if (QJL) {
-            // 3. q.g for all columns on the int8 tensor cores: A = G (+-1, built from the bit rows), B = the limbs;
-            //    MMA k index 4t'+j / 16+4t'+j  <->  d = 32t' + 8ks + j / + 4 + j
-            const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
-            const uint32_t* grow = a.g_rows + (size_t)seed_of(uid, hkv) * kQjlDim * 4;
-            const float inv0 = (2 * t < ncols) ? colinfo[2 * t].z : 0.f, inv1 = (2 * t + 1 < ncols) ? colinfo[2 * t + 1].z : 0.f;
-            __syncwarp();                                            // all reads of the query rows are done
-#pragma unroll
-            for (int mt = 0; mt < 4; ++mt) {
-                const uint32_t w0 = __ldg(grow + (16 * mt + g) * 4 + t), w1 = __ldg(grow + (16 * mt + g + 8) * 4 + t);
-                int chi[4] = {0, 0, 0, 0}, clo[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    const uint32_t x0 = w0 >> (8 * ks), x1 = w1 >> (8 * ks);
-                    const uint32_t a0 = pm1_bytes<0>(x0), a1 = pm1_bytes<0>(x1), a2 = pm1_bytes<4>(x0), a3 = pm1_bytes<4>(x1);
-                    imma_acc_s8s8(chi, a0, a1, a2, a3, bh[ks][0], bh[ks][1]);
-                    imma_acc_s8u8(clo, a0, a1, a2, a3, bl[ks][0], bl[ks][1]);
-                }
-                // C element j: projection 16mt + g + 8(j>>1), column 2t + (j&1)
-                if (2 * t < ncols) {
-                    qg_s[(2 * t) * 64 + 16 * mt + g] = (float)(chi[0] * 256 + clo[0]) * inv0;
-                    qg_s[(2 * t) * 64 + 16 * mt + g + 8] = (float)(chi[2] * 256 + clo[2]) * inv0;
-                }
-                if (2 * t + 1 < ncols) {
-                    qg_s[(2 * t + 1) * 64 + 16 * mt + g] = (float)(chi[1] * 256 + clo[1]) * inv1;
-                    qg_s[(2 * t + 1) * 64 + 16 * mt + g + 8] = (float)(chi[3] * 256 + clo[3]) * inv1;
-                }
-            }
-            __syncwarp();
-            // 4. quantise column g's 64 projections to int8 with one step; keep their sum even (it is halved)
-            //    (every lane runs the shuffles; lanes of unused columns work on zeros)
-            const bool mine = g < ncols;
-            float v[16];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (mine) x = *reinterpret_cast<const float4*>(qg_s + g * 64 + 16 * t + 4 * k);
-                v[4 * k] = x.x; v[4 * k + 1] = x.y; v[4 * k + 2] = x.z; v[4 * k + 3] = x.w;
-            }
-            float am = 0.f;
-#pragma unroll
-            for (int k = 0; k < 16; ++k) am = fmaxf(am, fabsf(v[k]));
-            am = fmaxf(am, __shfl_xor_sync(kFullMask, am, 1));
-            am = fmaxf(am, __shfl_xor_sync(kFullMask, am, 2));
-            const float step = am > 0.f ? am * (1.f / 127.f) : 1.f, rstep = 1.f / step;
-            int z[16], zsum = 0;
-#pragma unroll
-            for (int k = 0; k < 16; ++k) { z[k] = __float2int_rn(v[k] * rstep); zsum += z[k]; }
-            zsum += __shfl_xor_sync(kFullMask, zsum, 1);
-            zsum += __shfl_xor_sync(kFullMask, zsum, 2);
-            const int z_first = __shfl_sync(kFullMask, z[0], lane & ~3);     // the column's first projection (lane t = 0)
-            if (zsum & 1) {                                                  // uniform over the column's four lanes
-                const int fix = z_first < 127 ? 1 : -1;
-                if (t == 0) z[0] += fix;
-                zsum += fix;
-            }
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint32_t p01 = __byte_perm(z[4 * k], z[4 * k + 1], 0x5140), p23 = __byte_perm(z[4 * k + 2], z[4 * k + 3], 0x5140);
-                sg.z[k] = __byte_perm(p01, p23, 0x5410);
-            }
-            const float mycs = mine ? -2.f * step : 0.f;
-            const int myzh = zsum / 2;
-            // the thread's score columns are 2t and 2t+1: fetch their seeds and steps from those columns' lanes
-            sg.zq[0] = sg.zq[2] = __shfl_sync(kFullMask, myzh, 8 * t);
-            sg.zq[1] = sg.zq[3] = __shfl_sync(kFullMask, myzh, 8 * t + 4);
-            sg.cs0 = __shfl_sync(kFullMask, mycs, 8 * t);
-            sg.cs1 = __shfl_sync(kFullMask, mycs, 8 * t + 4);
-        }
-        __syncwarp();
+        const uint32_t (&qB)[8][2] = qo.qB;
+        const SignB& sg = qo.sg;
+        const float post0 = qo.post0, post1 = qo.post1;
 
         WarpState st;
 #pragma unroll
@@ -917,6 +1001,15 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
         map_v = map_k;
     } else {
         rc = make_nibble_map(&map_v, a.v_nib);
+        if (rc != OMNI_OK) return rc;
+    }
+    if (a.qprep) {
+        const int64_t units = a.B * a.Hkv * n_ctiles;
+        int64_t blocks = (units + 3) / 4;
+        if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+        if (a.with_qjl) qattn_prep_kernel<DT, true><<<(unsigned)blocks, 128, 0, st>>>(a, units);
+        else            qattn_prep_kernel<DT, false><<<(unsigned)blocks, 128, 0, st>>>(a, units);
+        rc = check_cuda(cudaGetLastError(), "qattn_prep_kernel launch");
         if (rc != OMNI_OK) return rc;
     }
     const bool one_col = (a.Hq / a.Hkv) * a.T == 1;
