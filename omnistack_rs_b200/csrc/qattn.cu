@@ -331,24 +331,35 @@ static int32_t validate(const AttnArgs& a, size_t ws_bytes) {
     return OMNI_OK;
 }
 
-enum KernelChoice { kAuto = 0, kLanePerKey = 1, kMma = 2 };
+enum KernelChoice { kAuto = 0, kLanePerKey = 1, kMma = 2, kUmma = 3 };
 
-// OMNI_QATTN_KERNEL=lane|mma forces one kernel (tests and profiling); default: by shape.
+// OMNI_QATTN_KERNEL=lane|mma|umma forces one kernel where it covers the call (tests and profiling); default: by shape.
 static KernelChoice kernel_choice_from_env() {
     const char* e = getenv("OMNI_QATTN_KERNEL");
     if (!e) return kAuto;
     if (e[0] == 'l') return kLanePerKey;
     if (e[0] == 'm') return kMma;
+    if (e[0] == 'u') return kUmma;
     return kAuto;
 }
+
+// Query columns per kv head from which the tcgen05 kernel is taken: it dequantises a key once for up to 128 columns,
+// the warp-level kernel once per eight.
+constexpr int64_t kUmmaMinColumns = 80;
 
 static int32_t launch(const AttnArgs& a, cudaStream_t st, size_t ws_bytes) {
     if (a.B == 0 || a.T == 0) return OMNI_OK;
     const KernelChoice choice = kernel_choice_from_env();
     // measured crossover: the tensor-core kernel wins from 128 keys on, and for shorter caches once the
     // lane-per-key kernel would need more than about a thousand warps
-    const bool use_mma = mma_eligible(a) &&
-                         (choice == kMma || (choice == kAuto && (a.S >= 128 || a.B * a.Hq * a.T >= 1024)));
+    const int64_t cols = (int64_t)(a.Hq / a.Hkv) * a.T;
+    const bool use_umma = umma_eligible(a) && (choice == kUmma || (choice == kAuto && cols >= kUmmaMinColumns && a.S >= 128));
+    const bool use_mma = !use_umma && mma_eligible(a) &&
+                         (choice == kMma || ((choice == kAuto || choice == kUmma) && (a.S >= 128 || a.B * a.Hq * a.T >= 1024)));
+    if (use_umma) {
+        const int32_t rc = launch_umma(a, st);
+        if (rc != OMNI_OK) return rc;
+    }
     if (use_mma) {
         AttnArgs m = a;
         if (a.n_splits > 1) {    // the ticket counters sit behind the partial states, the prepared query operands behind those
@@ -371,10 +382,10 @@ static int32_t launch(const AttnArgs& a, cudaStream_t st, size_t ws_bytes) {
         // stand-by that returns at once unless the codebooks are outside the fp16 table's range (decided on the
         // device by both kernels with the same test), so a persistent-size grid suffices there.
         AttnArgs l = a;
-        l.only_if_wide = use_mma ? 1 : 0;
+        l.only_if_wide = (use_mma || use_umma) ? 1 : 0;
         const int64_t n_work = a.B * a.Hq * a.T * a.n_splits;
         int64_t blocks = (n_work + kAttnWarps - 1) / kAttnWarps;
-        const int64_t cap = use_mma ? 148 * 8 : 148 * 64;
+        const int64_t cap = (use_mma || use_umma) ? 148 * 8 : 148 * 64;
         if (blocks > cap) blocks = cap;
         switch (a.q_dtype) {
             case OMNI_F32:  qattn_lane_per_key_kernel<OMNI_F32><<<(unsigned)blocks, kAttnWarps * 32, 0, st>>>(l); break;

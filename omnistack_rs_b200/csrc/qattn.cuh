@@ -35,9 +35,21 @@ struct AttnArgs {
 constexpr float kFp16CentroidLimit = 8.0f;
 __device__ __forceinline__ bool centroid_is_wide(float c) { return !(fabsf(c) < kFp16CentroidLimit); }
 
+// Factor the fp16 centroid tables are built with.  fp16 spacing relative to the value is smallest just below a power
+// of two, so the codebook is scaled to put its largest magnitude there (2.73 -> 3.996 for the Lloyd-Max codebook of
+// unit-variance data: the largest centroids round by 6.7e-4 instead of 9.8e-4; 4.6 -> 7.99: 1.1e-3 instead of
+// 1.95e-3).  The factor is taken back out of the scores through the query scale and out of the output row at the end.
+__device__ __forceinline__ float lut_scale_of(const float* cb) {
+    float m = 0.f;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) m = fmaxf(m, fabsf(__ldg(cb + c)));
+    if (!(m > 1e-30f) || !(m < kFp16CentroidLimit)) return 1.f;
+    return exp2f(ceilf(log2f(m))) * (1.f - 1.f / 1024.f) / m;
+}
+
 constexpr int kWsStride = 132;     // floats per split-K partial: 128 accumulators, max, sum, 2 pad
 constexpr size_t kWorkCounterBytes = 4096;   // kSeeds (the most kv heads a call may have) 32-bit counters
-constexpr size_t kPrepBytesPerUnit = 28 * 4 * 32;   // prepared query operands of one work item: 28 words per lane
+constexpr size_t kPrepBytesPerUnit = 32 * 4 * 32;   // prepared query operands of one work item: 32 words per lane
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -53,6 +65,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Tensor-core kernel (qattn_mma.cu): shapes it covers, and its launcher.
 bool mma_eligible(const AttnArgs& a);
 int32_t launch_mma(const AttnArgs& a, cudaStream_t st);
+// tcgen05 kernel (qattn_umma.cu): kv heads with many query columns, V rows in the reference layout.
+bool umma_eligible(const AttnArgs& a);
+int32_t launch_umma(const AttnArgs& a, cudaStream_t st);
 // One-warp kernel that lets a bounded mbarrier wait run out on purpose (nothing arrives on its barrier).
 int32_t launch_wait_probe(uint32_t limit, int32_t* status, cudaStream_t st);
 

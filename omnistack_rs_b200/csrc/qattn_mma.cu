@@ -135,7 +135,10 @@ __device__ __forceinline__ uint32_t lut_at(uint32_t lut_lane, uint32_t w) {
 // The 64 sign bits of a key go to the int8 tensor cores: A = -bit built in registers (a multiply spreads
 // 4 bits to the 4 byte MSBs, PRMT replicates them), B = q.g quantised to int8 per column.
 struct SignB {
-    uint32_t z[4];          // int8 x4: q.g of column g, projections 16t .. 16t+15
+    uint32_t zh[4], zl[4];  // q.g of column g, projections 16t .. 16t+15, as 16-bit integers z = 256 * zh + zl
+                            // (zh signed, zl unsigned; four per word).  One 8-bit limb is not enough: the quantisation
+                            // noise of the 64-term sum is multiplied by the key's residual norm, and heavy-tailed
+                            // data (outlier channels) has norms of 10 and more
     int zq[4];              // accumulator seed (sum of z)/2 for columns 2t, 2t+1, 2t, 2t+1
     float cs0, cs1;         // -2 * quantisation step of columns 2t, 2t+1
 };
@@ -293,11 +296,16 @@ __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState&
     if (QJL) {
         // sum_i s_i z_i = -2 * (sum_i (-bit_i) z_i + Z/2): the seed Z/2 rides in as the MMA addend
         const uint32_t sa8 = kb.sa >> 8, sb8 = kb.sb >> 8;
-        int d0[4], d1[4];
-        imma_s8(d0, neg_bits_s8<0>(kb.sa), neg_bits_s8<0>(kb.sb), neg_bits_s8<4>(kb.sa), neg_bits_s8<4>(kb.sb),
-                sg.z[0], sg.z[1], sg.zq);
-        imma_s8(d1, neg_bits_s8<0>(sa8), neg_bits_s8<0>(sb8), neg_bits_s8<4>(sa8), neg_bits_s8<4>(sb8),
-                sg.z[2], sg.z[3], d0);
+        const uint32_t a0 = neg_bits_s8<0>(kb.sa), a1 = neg_bits_s8<0>(kb.sb), a2 = neg_bits_s8<4>(kb.sa), a3 = neg_bits_s8<4>(kb.sb);
+        const uint32_t a4 = neg_bits_s8<0>(sa8), a5 = neg_bits_s8<0>(sb8), a6 = neg_bits_s8<4>(sa8), a7 = neg_bits_s8<4>(sb8);
+        int dh[4] = {0, 0, 0, 0}, dl[4] = {sg.zq[0], sg.zq[1], sg.zq[2], sg.zq[3]};
+        imma_acc_s8s8(dh, a0, a1, a2, a3, sg.zh[0], sg.zh[1]);
+        imma_acc_s8u8(dl, a0, a1, a2, a3, sg.zl[0], sg.zl[1]);
+        imma_acc_s8s8(dh, a4, a5, a6, a7, sg.zh[2], sg.zh[3]);
+        imma_acc_s8u8(dl, a4, a5, a6, a7, sg.zl[2], sg.zl[3]);
+        int d1[4];
+        d1[0] = dh[0] * 256 + dl[0]; d1[2] = dh[2] * 256 + dl[2];
+        if (!ONECOL) { d1[1] = dh[1] * 256 + dl[1]; d1[3] = dh[3] * 256 + dl[3]; }
         s00 = post0 * fmaf(kb.na * sg.cs0, (float)d1[0], cd[0] + ce[0]);
         s80 = post0 * fmaf(kb.nb * sg.cs0, (float)d1[2], cd[2] + ce[2]);
         if (!ONECOL) {
@@ -342,11 +350,22 @@ __device__ __forceinline__ void process_key_block(const KeyBlock& kb, WarpState&
     }
     const float p00 = ex2_approx(s00 - st.m0), p80 = ex2_approx(s80 - st.m0);
     const float p01 = ONECOL ? 0.f : ex2_approx(s01 - st.m1), p81 = ONECOL ? 0.f : ex2_approx(s81 - st.m1);
+    // The weights enter the V product rounded to fp16; the normaliser sums the SAME rounded values, so a key that
+    // carries the whole softmax returns its V row exactly instead of scaled by the rounding of its weight.
+    const uint32_t ph0 = pack_half2(p00, p01), ph1 = pack_half2(p80, p81);
+#ifndef OMNI_L_FROM_FP32
+    {
+        const __half2 h0 = *reinterpret_cast<const __half2*>(&ph0), h1 = *reinterpret_cast<const __half2*>(&ph1);
+        st.l0 += __low2float(h0) + __low2float(h1);
+        if (!ONECOL) st.l1 += __high2float(h0) + __high2float(h1);
+    }
+#else
     st.l0 += p00 + p80;
     if (!ONECOL) st.l1 += p01 + p81;
+#endif
     // P^T as the B operand: transpose the two 8x8 (key x column) blocks across the warp
-    const uint32_t pb0 = movmatrix_trans(pack_half2(p00, p01));
-    const uint32_t pb1 = movmatrix_trans(pack_half2(p80, p81));
+    const uint32_t pb0 = movmatrix_trans(ph0);
+    const uint32_t pb1 = movmatrix_trans(ph1);
     // V: index byte = nibble of key A | nibble of key B << 4 (the pair layout stores exactly these bytes)
     {
         const uint32_t A[2] = {kb.v0.x, kb.v0.y}, B[2] = {kb.v1.x, kb.v1.y};
@@ -377,15 +396,16 @@ struct QueryOperands {
     SignB sg;
     float post0, post1;
 };
-constexpr int kPrepWords = 28;              // 16 + 4 + 2 + 2 + 2 words per lane, padded to seven 16-byte vectors
+constexpr int kPrepWords = 32;              // 16 + 4 + 4 + 2 + 2 + 2 words per lane, padded to eight 16-byte vectors
 static_assert(kPrepBytesPerUnit == kPrepWords * 4 * 32, "prepared operands: size used by the workspace layout");
 
 // Builds them from the query rows of (user b, kv head hkv, columns col0 .. col0 + ncols).  `qrow` is this warp's
 // shared scratch (8 x 128 fp32 query rows, reused for the q.g projections) and `colinfo` the per-column scalars
 // behind it.  Every lane of the warp must call.
+// `inv_lut` = 1 / lut_scale_of(the head's codebook): the score operands carry it, the sign correction does not.
 template <int DT, bool QJL>
 __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t b, int hkv, int col0, int ncols, int Gq, float qs,
-                                                     float* qrow, float4* colinfo, int lane, QueryOperands& qo) {
+                                                     float inv_lut, float* qrow, float4* colinfo, int lane, QueryOperands& qo) {
     const int g = lane >> 2, t = lane & 3;
     float* qg_s = qrow;
     uint32_t (&qB)[8][2] = qo.qB;
@@ -400,7 +420,7 @@ __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t 
         if (a.rotate_q) wht128_warp(qv, lane);                  // the rotation folded into the query (fp32, not rounded)
         const float amax = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3]))));
         // fp16 operands stay below 2^10 in magnitude; the power of two is re-applied to the scores
-        const float mx = amax * fabsf(qs);
+        const float mx = amax * fabsf(qs) * inv_lut;
         float post = 1.f;
         if (mx > 1024.f) post = exp2f(ceilf(log2f(mx * (1.f / 1024.f))));
         const float f = qs / post;
@@ -408,7 +428,7 @@ __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t 
         const int E = (__float_as_uint(amax) >> 23) & 0xFF;
         const float sq = (E < 16 || E == 255) ? 0.f : __uint_as_float(((uint32_t)(267 - E) << 23) | 0x7F8000u);
         *reinterpret_cast<float4*>(qrow + c * 128 + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
-        if (lane == 0) colinfo[c] = make_float4(f, post, sq > 0.f ? kQjlCoef * f / sq : 0.f, sq);
+        if (lane == 0) colinfo[c] = make_float4(f * inv_lut, post, sq > 0.f ? kQjlCoef * f / sq : 0.f, sq);
     }
     __syncwarp();
     // 2. thread (g, t) owns column g: its 32 dims d = 32t .. 32t+31 as fp16 (scores) and as int8 limbs (q.g)
@@ -443,7 +463,7 @@ __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t 
     if (2 * t < ncols) post0 = colinfo[2 * t].y;
     if (2 * t + 1 < ncols) post1 = colinfo[2 * t + 1].y;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) { sg.z[k] = 0u; sg.zq[k] = 0; }
+    for (int k = 0; k < 4; ++k) { sg.zh[k] = 0u; sg.zl[k] = 0u; sg.zq[k] = 0; }
     sg.cs0 = 0.f; sg.cs1 = 0.f;
     if (QJL) {
         // 3. q.g for all columns on the int8 tensor cores: A = G (+-1, built from the bit rows), B = the limbs;
@@ -474,7 +494,7 @@ __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t 
             }
         }
         __syncwarp();
-        // 4. quantise column g's 64 projections to int8 with one step; keep their sum even (it is halved)
+        // 4. quantise column g's 64 projections to 16-bit integers with one step; keep their sum even (it is halved)
         //    (every lane runs the shuffles; lanes of unused columns work on zeros)
         const bool mine = g < ncols;
         float v[16];
@@ -489,7 +509,7 @@ __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t 
         for (int k = 0; k < 16; ++k) am = fmaxf(am, fabsf(v[k]));
         am = fmaxf(am, __shfl_xor_sync(kFullMask, am, 1));
         am = fmaxf(am, __shfl_xor_sync(kFullMask, am, 2));
-        const float step = am > 0.f ? am * (1.f / 127.f) : 1.f, rstep = 1.f / step;
+        const float step = am > 0.f ? am * (1.f / 32767.f) : 1.f, rstep = 1.f / step;
         int z[16], zsum = 0;
 #pragma unroll
         for (int k = 0; k < 16; ++k) { z[k] = __float2int_rn(v[k] * rstep); zsum += z[k]; }
@@ -497,14 +517,16 @@ __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t 
         zsum += __shfl_xor_sync(kFullMask, zsum, 2);
         const int z_first = __shfl_sync(kFullMask, z[0], lane & ~3);     // the column's first projection (lane t = 0)
         if (zsum & 1) {                                                  // uniform over the column's four lanes
-            const int fix = z_first < 127 ? 1 : -1;
+            const int fix = z_first < 32767 ? 1 : -1;
             if (t == 0) z[0] += fix;
             zsum += fix;
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
+            // bytes 0 (low limb) and 1 (high limb, arithmetic: z = 256 * (z >> 8) + (z & 255)) of four integers
             const uint32_t p01 = __byte_perm(z[4 * k], z[4 * k + 1], 0x5140), p23 = __byte_perm(z[4 * k + 2], z[4 * k + 3], 0x5140);
-            sg.z[k] = __byte_perm(p01, p23, 0x5410);
+            sg.zl[k] = __byte_perm(p01, p23, 0x5410);
+            sg.zh[k] = __byte_perm(p01, p23, 0x7632);
         }
         const float mycs = mine ? -2.f * step : 0.f;
         const int myzh = zsum / 2;
@@ -522,19 +544,21 @@ __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t 
 __device__ __forceinline__ void pack_query_operands(const QueryOperands& qo, uint4 (&v)[kPrepWords / 4]) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) v[k] = make_uint4(qo.qB[2 * k][0], qo.qB[2 * k][1], qo.qB[2 * k + 1][0], qo.qB[2 * k + 1][1]);
-    v[4] = make_uint4(qo.sg.z[0], qo.sg.z[1], qo.sg.z[2], qo.sg.z[3]);
-    v[5] = make_uint4((uint32_t)qo.sg.zq[0], (uint32_t)qo.sg.zq[1], __float_as_uint(qo.sg.cs0), __float_as_uint(qo.sg.cs1));
-    v[6] = make_uint4(__float_as_uint(qo.post0), __float_as_uint(qo.post1), 0u, 0u);
+    v[4] = make_uint4(qo.sg.zh[0], qo.sg.zh[1], qo.sg.zh[2], qo.sg.zh[3]);
+    v[5] = make_uint4(qo.sg.zl[0], qo.sg.zl[1], qo.sg.zl[2], qo.sg.zl[3]);
+    v[6] = make_uint4((uint32_t)qo.sg.zq[0], (uint32_t)qo.sg.zq[1], __float_as_uint(qo.sg.cs0), __float_as_uint(qo.sg.cs1));
+    v[7] = make_uint4(__float_as_uint(qo.post0), __float_as_uint(qo.post1), 0u, 0u);
 }
 __device__ __forceinline__ void unpack_query_operands(const uint4 (&v)[kPrepWords / 4], QueryOperands& qo) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         qo.qB[2 * k][0] = v[k].x; qo.qB[2 * k][1] = v[k].y; qo.qB[2 * k + 1][0] = v[k].z; qo.qB[2 * k + 1][1] = v[k].w;
     }
-    qo.sg.z[0] = v[4].x; qo.sg.z[1] = v[4].y; qo.sg.z[2] = v[4].z; qo.sg.z[3] = v[4].w;
-    qo.sg.zq[0] = qo.sg.zq[2] = (int)v[5].x; qo.sg.zq[1] = qo.sg.zq[3] = (int)v[5].y;
-    qo.sg.cs0 = __uint_as_float(v[5].z); qo.sg.cs1 = __uint_as_float(v[5].w);
-    qo.post0 = __uint_as_float(v[6].x); qo.post1 = __uint_as_float(v[6].y);
+    qo.sg.zh[0] = v[4].x; qo.sg.zh[1] = v[4].y; qo.sg.zh[2] = v[4].z; qo.sg.zh[3] = v[4].w;
+    qo.sg.zl[0] = v[5].x; qo.sg.zl[1] = v[5].y; qo.sg.zl[2] = v[5].z; qo.sg.zl[3] = v[5].w;
+    qo.sg.zq[0] = qo.sg.zq[2] = (int)v[6].x; qo.sg.zq[1] = qo.sg.zq[3] = (int)v[6].y;
+    qo.sg.cs0 = __uint_as_float(v[6].z); qo.sg.cs1 = __uint_as_float(v[6].w);
+    qo.post0 = __uint_as_float(v[7].x); qo.post1 = __uint_as_float(v[7].y);
 }
 
 // Preparation launch of split-K calls: one warp per (user, kv head, tile of 8 query columns) builds the item's
@@ -554,7 +578,8 @@ __global__ void __launch_bounds__(128) qattn_prep_kernel(AttnArgs a, int64_t n_u
         const int64_t b = unit / n_ctiles / a.Hkv;
         const int ncols = ncols_all - col0 < 8 ? ncols_all - col0 : 8;
         QueryOperands qo;
-        build_query_operands<DT, QJL>(a, b, hkv, col0, ncols, Gq, qs, qrow, colinfo, lane, qo);
+        const float inv_lut = 1.f / lut_scale_of(a.codebooks + (a.cb_per_head ? hkv * 16 : 0));
+        build_query_operands<DT, QJL>(a, b, hkv, col0, ncols, Gq, qs, inv_lut, qrow, colinfo, lane, qo);
         uint4 v[kPrepWords / 4];
         pack_query_operands(qo, v);
         uint4* dst = reinterpret_cast<uint4*>(a.qprep) + unit * (kPrepWords / 4) * 32 + lane;
@@ -619,12 +644,14 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         for (int i = threadIdx.x; i < n_cb; i += blockDim.x) wide = wide || centroid_is_wide(__ldg(a.codebooks + i));
         if (__syncthreads_or(wide)) return;
     }
+    const float lut_scale = lut_scale_of(a.codebooks + (a.cb_per_head ? cb_head * 16 : 0));
+    const float inv_lut = 1.f / lut_scale;
     {
         const float* cb = a.codebooks + (a.cb_per_head ? cb_head * 16 : 0);
         uint32_t* lut = reinterpret_cast<uint32_t*>(smem + lut_off);
         for (int i = threadIdx.x; i < 256 * 8; i += blockDim.x) {       // four lanes' copies of an entry per store
             const int byte = i >> 3, quad = i & 7;
-            const uint32_t v = pack_half2(__ldg(cb + (byte & 15)), __ldg(cb + (byte >> 4)));
+            const uint32_t v = pack_half2(__ldg(cb + (byte & 15)) * lut_scale, __ldg(cb + (byte >> 4)) * lut_scale);
             *reinterpret_cast<uint4*>(lut + byte * 64 + 4 * quad) = make_uint4(v, v, v, v);
         }
     }
@@ -718,7 +745,7 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
             for (int k = 0; k < kPrepWords / 4; ++k) v[k] = __ldg(src + 32 * k);
             unpack_query_operands(v, qo);
         } else {
-            build_query_operands<DT, QJL>(a, b, hkv, col0, ncols, Gq, qs, qrow, colinfo, lane, qo);
+            build_query_operands<DT, QJL>(a, b, hkv, col0, ncols, Gq, qs, inv_lut, qrow, colinfo, lane, qo);
         }
         const uint32_t (&qB)[8][2] = qo.qB;
         const SignB& sg = qo.sg;
@@ -808,11 +835,11 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
             float mul;
             if (a.n_splits == 1) {
                 dst = a.out + qrow * kHeadDim + 16 * g;
-                mul = l > 0.f ? 1.f / l : 0.f;
+                mul = l > 0.f ? inv_lut / l : 0.f;
             } else {
                 float* w = a.ws + (qrow * a.n_splits + split) * kWsStride;
                 dst = w + 16 * g;
-                mul = 1.f;
+                mul = inv_lut;
                 if (real && g == 0) { w[128] = m * 0.6931471805599453f; w[129] = l; }   // max back in natural-log units
             }
             float v[16];                          // d = 16g + i, i = 4mp + e  (m-tiles 2mp, 2mp+1)

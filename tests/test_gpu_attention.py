@@ -409,3 +409,27 @@ def test_cache_with_paired_v_follows_appends(dev):
         q = torch.randn(B, 4, 1, 128, generator=gen).to(torch.bfloat16).to(dev)
         assert torch.equal(fast.attend(q), plain.attend(q)), n
     assert not torch.equal(fast.v_nib, plain.v_nib)
+
+
+def test_prepared_query_operands_match_inline_ones(dev, monkeypatch):
+    """Split-K calls with many work items build the query operands once per (user, kv head, column tile) in a launch of
+    their own and every split fetches them; small calls build them inline.  Both ways give the same bits."""
+    fa = attn_mod()
+    kn, kq, kr, vn, cb, gen = make_cache(3, 2, 333, seed=12, user_id=9, per_head=False, outliers=True)
+    cache = to_dev(dev, kn, kq, kr, vn, cb)
+    lens = torch.tensor([333, 40, 200], dtype=torch.int32, device=dev)
+    for T in (1, 3):                                                  # 4 and 12 query columns per kv head (two tiles)
+        q = torch.randn(3, 8, T, 128, generator=gen).to(torch.bfloat16)
+        outs = {}
+        for flag in ("0", "1"):
+            monkeypatch.setenv("OMNI_QATTN_PREP", flag)
+            outs[flag] = [fa.omni_attn(q.to(dev), *cache, user_id=9, n_splits=ns, seq_lens=lens, rotate_q=bool(T == 3))
+                          for ns in (2, 5)]
+        for a, b in zip(outs["0"], outs["1"]):
+            assert torch.equal(a, b)
+        qq = orc.wht128(q.float()) if T == 3 else q
+        for b_ in range(3):
+            n = int(lens[b_])
+            want = orc.decode_attention(qq[b_:b_ + 1], kn[b_:b_ + 1, :, :n], kq[b_:b_ + 1, :, :n], kr[b_:b_ + 1, :, :n],
+                                        vn[b_:b_ + 1, :, :n], cb, 9)
+            assert (outs["1"][0][b_:b_ + 1].cpu() - want).abs().max() <= ATOL
