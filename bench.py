@@ -41,12 +41,15 @@ WORKLOADS = {
     # name: (description, Hq, Hkv, S, users per GPU)
     "serve": ("config4-box-serving-shard: 16384 users/GPU x 32 kv heads x 2048 keys, 1 bf16 query/user/step", 32, 32, 2048, USERS_PER_GPU),
     "decode64": ("config1: 64 users x 8 heads x 50 keys", 8, 8, 50, 64),
-    "gqa": ("config2: 256 users, 32 q / 8 kv heads, context U[1024,8192]", 32, 8, 8192, 256),
+    "gqa": ("config2: 256 users, 32 q / 8 kv heads, context U[1024,8192], K/V N(0,1) with 4 channels x8 before the rotation", 32, 8, 8192, 256),
     # the reference's own headline benchmark shape (scripts/run_criteo_benchmark.py: 64 users per query, 32 q / 8 kv heads,
     # 50 keys, per-user LoRA query update on, V aliased to K's nibbles); published: 104,571.3 users/s on an A10
     "criteo": ("reference headline shape: 64 users/query, 32 q / 8 kv heads, 50 keys, LoRA-Q on, V = K nibbles", 32, 8, 50, 64),
     # the other codec kernels, one after the other (reporting only): rotation, dequantisation, fp32 quantize, calibration
     "codec": ("codec kernels: rotate / dequantize / quantize (fp32, rotated input) / Lloyd-Max fit, 2048 users x 8 heads x 256 tokens", 8, 8, 256, 2048),
+    # grouped queries over several tokens (speculative decoding / short prefill; reporting only): 128 query columns per
+    # kv head, the shape the tcgen05 kernel exists for
+    "mtok": ("multi-token grouped queries: 64 users, 32 q / 8 kv heads, 32 query tokens, 2048 keys", 32, 8, 2048, 64),
     # quantize-append (reporting only): 8 kv heads, 256 new bf16 tokens per user, K and V
     "append": ("config3: 4096 users x 256 new tokens x 8 heads, bf16 K and V, N(0,1) with 1% x10", 8, 8, 256, 4096),
 }
@@ -116,7 +119,7 @@ def dist_env():
     return rank, world, local
 
 
-def build_resident_cache(dev, Hkv, S, n_res, seed, lens=None):
+def build_resident_cache(dev, Hkv, S, n_res, seed, lens=None, outliers=False):
     """Fill a resident packed cache with N(0,1) K/V pushed through the library's own
     rotate+quantize kernel, chunk by chunk (set-up, untimed).  V's nibble rows are then put into the
     pair layout of a serving cache (every complete group of eight keys below the user's length)."""
@@ -125,6 +128,16 @@ def build_resident_cache(dev, Hkv, S, n_res, seed, lens=None):
     gen = torch.Generator(device=dev).manual_seed(seed)
     cb = torch.tensor([-2.733, -2.069, -1.618, -1.256, -0.9424, -0.6568, -0.3881, -0.1284,
                        0.1284, 0.3881, 0.6568, 0.9424, 1.256, 1.618, 2.069, 2.733], device=dev)  # 16-level Lloyd-Max, unit Gaussian
+    chans = None
+    if outliers:
+        # configuration 2: four channels (the same for every row) carry 8x the scale before the rotation; one
+        # shared codebook fitted by the library's Lloyd-Max kernel on a million rotated samples
+        from omnistack_rs_b200.kernels.hadamard import rotate_queries
+        from omnistack_rs_b200.quantization import calibrate_codebook
+        chans = torch.randperm(128, generator=torch.Generator().manual_seed(1))[:4].to(dev)
+        x = torch.randn(64, Hkv, 16, 128, generator=torch.Generator(device=dev).manual_seed(seed + 7), device=dev)
+        x[..., chans] *= 8.0
+        cb = calibrate_codebook(rotate_queries(x).reshape(-1)[: 1 << 20].contiguous()).to(dev)
     k_nib = torch.empty(n_res, Hkv, S, 64, dtype=torch.uint8, device=dev)
     k_qjl = torch.empty(n_res, Hkv, S, 8, dtype=torch.uint8, device=dev)
     k_norms = torch.empty(n_res, Hkv, S, dtype=torch.float32, device=dev)
@@ -135,8 +148,12 @@ def build_resident_cache(dev, Hkv, S, n_res, seed, lens=None):
     for u0 in range(0, n_res, chunk):
         n = min(chunk, n_res - u0)
         x = torch.randn(n, Hkv, S, 128, generator=gen, device=dev, dtype=torch.bfloat16)
+        if chans is not None:
+            x[..., chans] *= 8.0
         _quantize_into(x, cb, 0, True, k_nib[u0:u0 + n], k_qjl[u0:u0 + n], k_norms[u0:u0 + n], Hkv * S, S, None, 0)
         x = torch.randn(n, Hkv, S, 128, generator=gen, device=dev, dtype=torch.bfloat16)
+        if chans is not None:
+            x[..., chans] *= 8.0
         _quantize_into(x, cb, 0, True, v_nib[u0:u0 + n], sq[:n], sn[:n], Hkv * S, S, None, 0)
     del sq, sn
     if PAIR_V:
@@ -220,7 +237,8 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
         lens = torch.randint(1024, 8193, (users,), generator=g).to(torch.int32)
     if lens is not None and n_res < users:
         raise SystemExit("ragged lengths need every user resident (the pair layout of V follows each user's length)")
-    k_nib, k_qjl, k_norms, v_nib, cb = build_resident_cache(dev, Hkv, S, n_res, seed=1234 + rank, lens=lens)
+    k_nib, k_qjl, k_norms, v_nib, cb = build_resident_cache(dev, Hkv, S, n_res, seed=1234 + rank, lens=lens,
+                                                            outliers=(workload == "gqa"))
     slots = (torch.arange(users, dtype=torch.int32) % n_res).to(dev) if n_res < users else None
     lens_dev = None if lens is None else lens.to(dev)
     keys_per_step = int(lens.sum()) * Hkv if lens is not None else users * Hkv * S
@@ -570,6 +588,64 @@ def run_criteo(args):
     }))
 
 
+def run_mtok(args):
+    """Attention of 32 query tokens per user (128 query columns per kv head) over a 2,048-key packed cache: the
+    tcgen05 kernel (default for 80 or more columns) and the warp-level kernel (eight columns per tile) on the same
+    inputs.  Single GPU, reporting only."""
+    from omnistack_rs_b200 import _lib
+    from omnistack_rs_b200.kernels.fused_attention import omni_attn
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    desc, Hq, Hkv, S, users = WORKLOADS["mtok"]
+    if args.users:
+        users = args.users
+    T = 32
+    global PAIR_V
+    PAIR_V = False                                     # the tcgen05 kernel reads the reference layout of V
+    k_nib, k_qjl, k_norms, v_nib, cb = build_resident_cache(dev, Hkv, S, users, seed=77)
+    q = torch.randn(users, Hq, T, 128, device=dev, dtype=torch.bfloat16)
+    peak, peak_kind = measured_peak()
+    alg = users * Hkv * S * BYTES_PER_KEY + users * Hq * T * 768
+    sampler = ClockSampler(local)
+    sampler.start()
+    kernels = {}
+    for name, env in (("tcgen05", None), ("warp_level_tiles", "mma")):
+        if env is None:
+            os.environ.pop("OMNI_QATTN_KERNEL", None)
+        else:
+            os.environ["OMNI_QATTN_KERNEL"] = env
+        for _ in range(args.warmup):
+            out = omni_attn(q, k_nib, k_qjl, k_norms, v_nib, cb, user_id=0)
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            out = omni_attn(q, k_nib, k_qjl, k_norms, v_nib, cb, user_id=0)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / args.steps
+        kernels[name] = {"ms": ms, "gb_per_s": alg / (ms * 1e-3) / 1e9, "checksum": float(out.abs().mean())}
+    os.environ.pop("OMNI_QATTN_KERNEL", None)
+    clocks = sampler.stop()
+    _lib.check_device_status(dev)
+    lead = kernels["tcgen05"]
+    print(json.dumps({
+        "metric": "query_tokens_per_sec_multi_token_attention", "value": users * T / (lead["ms"] * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": lead["ms"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": desc, "users": users, "q_heads": Hq, "kv_heads": Hkv, "query_tokens": T, "keys": S,
+                   "l2": "inputs larger than L2" if alg > 2e8 else "inputs smaller than L2"},
+        "roofline": {"bound": "hbm", "achieved": lead["gb_per_s"], "peak": peak, "unit": "GB/s", "frac": lead["gb_per_s"] / peak,
+                     "peak_source": peak_kind, "traffic": None, "kernel": "qattn_umma_kernel",
+                     "note": "the kernel is bound by its serial softmax / dequantise phases, not by HBM"},
+        "kernels": kernels, "speedup_over_warp_level_tiles": kernels["warp_level_tiles"]["ms"] / lead["ms"],
+        "cpu_baseline": None, "e2e": None, "gpu_launches": 2 * args.steps, "clocks": clocks,
+    }))
+
+
 def run_codec(args):
     """Times the codec kernels that no serving workload exercises, each against its algorithmic bytes (single GPU)."""
     from omnistack_rs_b200 import _lib
@@ -723,6 +799,8 @@ def main():
         run_criteo(args)
     elif args.workload == "codec":
         run_codec(args)
+    elif args.workload == "mtok":
+        run_mtok(args)
     else:
         run_ours(args)
 
