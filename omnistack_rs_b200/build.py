@@ -19,7 +19,7 @@ OBJ_DIR = os.path.join(CSRC, "_obj")
 LIB_PATH = os.path.join(CSRC, "libomni_b200.so")
 SOURCES = ["runtime.cu", "codec.cu", "codec_fast.cu", "qattn.cu", "qattn_mma.cu", "qattn_umma.cu", "lora_q.cu",
            "lloyd_max.cu", "qjl_bool.cu"]
-HEADERS = ["common.cuh", "qattn.cuh", "codec_fast.cuh", os.path.join("..", "..", "include", "omni_b200.h")]
+HEADERS = ["common.cuh", "qattn.cuh", "codec_fast.cuh", "codec_tc.cuh", os.path.join("..", "..", "include", "omni_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 LINK_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-cudart", "static", "-Xcompiler", "-fPIC"]
 

@@ -20,10 +20,11 @@ def dev():
     return torch.device("cuda:0")
 
 
-@pytest.fixture(autouse=True, params=["fast", "scan"])
+@pytest.fixture(autouse=True, params=["tc", "warp", "scan"])
 def quant_kernel_choice(request, monkeypatch):
-    """Every case runs once per quantize kernel: the 8-rows-per-warp tensor-core kernel (default)
-    and the one-row-per-warp scan kernel that OMNI_QUANT_KERNEL=scan forces."""
+    """Every case runs once per quantize kernel: the row-per-thread kernel with tcgen05 projections
+    (OMNI_QUANT_KERNEL=tc), the 8-rows-per-warp kernel with mma.sync projections (=warp, the default) and the
+    one-row-per-warp scan kernel (=scan)."""
     monkeypatch.setenv("OMNI_QUANT_KERNEL", request.param)
     return request.param
 
