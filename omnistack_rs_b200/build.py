@@ -17,9 +17,10 @@ import sys
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 OBJ_DIR = os.path.join(CSRC, "_obj")
 LIB_PATH = os.path.join(CSRC, "libomni_b200.so")
-SOURCES = ["runtime.cu", "codec.cu", "codec_fast.cu", "qattn.cu", "qattn_mma.cu", "qattn_umma.cu", "lora_q.cu",
+SOURCES = ["runtime.cu", "codec.cu", "codec_fast.cu", "qattn.cu", "qattn_mma.cu", "qattn_mma_lora.cu", "qattn_umma.cu", "lora_q.cu",
            "lloyd_max.cu", "qjl_bool.cu"]
-HEADERS = ["common.cuh", "qattn.cuh", "codec_fast.cuh", "codec_tc.cuh", os.path.join("..", "..", "include", "omni_b200.h")]
+# qattn_mma.cu is also a header: qattn_mma_lora.cu includes it
+HEADERS = ["common.cuh", "qattn.cuh", "codec_fast.cuh", "codec_tc.cuh", "qattn_mma.cu", os.path.join("..", "..", "include", "omni_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 LINK_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-cudart", "static", "-Xcompiler", "-fPIC"]
 

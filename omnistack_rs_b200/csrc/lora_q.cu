@@ -3,11 +3,14 @@
 //   q_eff[b] = q[b] exactly                                                                  idx_b <  0
 // An index at or past the number of adapters leaves the row unchanged too and raises the status word to
 // OMNI_STATUS_BAD_INDEX, so the host needs no synchronising range check before the launch.
-// One CTA of 1024 threads per (user, token).  Down projection: the warps split the `rank` rows of A between
-// them (several warps per row when there are more warps than rows) and reduce over the hidden axis.  Up
+// The attention kernels apply the same update inside their prologues (LoraFold in qattn.cuh); this kernel serves
+// omni_lora_q and the calls whose attention kernel takes no folded update.
+// One CTA of 1024 threads per (user, token).  Down projection: the warps take the `rank` rows of A in turn and
+// reduce over the hidden axis (lora_down_row, shared with the folded form so that both agree bit for bit).  Up
 // projection: a thread owns output elements o, o + 1024, ... and reads its rows of B as 16-byte vectors; those
 // loads do not depend on the down projection and are issued before the barrier that publishes it.  fp32 throughout.
 #include "common.cuh"
+#include "qattn.cuh"
 
 namespace omni {
 
@@ -26,7 +29,6 @@ template <int DT>
 __global__ void __launch_bounds__(kLoraThreads) lora_q_kernel(const void* q, const float* x, const float* la, const float* lb,
                                                              const int32_t* idx, int n_adapters, float alpha, int Hq, int T,
                                                              int hidden, int rank, float* out, int32_t* status) {
-    __shared__ float part[kLoraMaxRank][kLoraWarps + 1];   // partial sums of the down projection
     __shared__ float down[kLoraMaxRank];
     const int b = blockIdx.x / T, t = blockIdx.x % T;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -43,20 +45,11 @@ __global__ void __launch_bounds__(kLoraThreads) lora_q_kernel(const void* q, con
         }
         return;
     }
-    // warps_per_row warps share one row of A (a power of two so that the pieces tile the warp count)
-    int warps_per_row = 1;
-    while (warps_per_row * 2 * rank <= kLoraWarps) warps_per_row *= 2;
     const float* xr = x + ((int64_t)b * T + t) * hidden;
     const float* a = la + (int64_t)li * rank * hidden;
-    for (int r0 = 0; r0 < rank; r0 += kLoraWarps / warps_per_row) {
-        const int r = r0 + warp / warps_per_row, piece = warp % warps_per_row;
-        if (r < rank) {
-            float acc = 0.f;
-            for (int k = piece * 32 + lane; k < hidden; k += 32 * warps_per_row) acc = fmaf(xr[k], a[(int64_t)r * hidden + k], acc);
-#pragma unroll
-            for (int m = 16; m >= 1; m >>= 1) acc += __shfl_xor_sync(kFullMask, acc, m);
-            if (lane == 0) part[r][piece] = acc;
-        }
+    for (int r = warp; r < rank; r += kLoraWarps) {
+        const float acc = lora_down_row(xr, a + (int64_t)r * hidden, hidden, lane);
+        if (lane == 0) down[r] = acc;
     }
     const float* bm = lb + (int64_t)li * n_out * rank;
     const bool vec = (rank % 4 == 0) && ((reinterpret_cast<uintptr_t>(lb) & 15) == 0);
@@ -68,15 +61,7 @@ __global__ void __launch_bounds__(kLoraThreads) lora_q_kernel(const void* q, con
         const float* br = bm + (int64_t)(live ? o : 0) * rank;
         float4 first = make_float4(0.f, 0.f, 0.f, 0.f);
         if (vec && live) first = *reinterpret_cast<const float4*>(br);   // in flight across the barrier below
-        if (o0 == 0) {
-            __syncthreads();
-            if (threadIdx.x < rank) {
-                float sum = 0.f;
-                for (int p = 0; p < warps_per_row; ++p) sum += part[threadIdx.x][p];
-                down[threadIdx.x] = sum;
-            }
-            __syncthreads();
-        }
+        if (o0 == 0) __syncthreads();
         if (!live) continue;
         float up = 0.f;
         if (vec) {

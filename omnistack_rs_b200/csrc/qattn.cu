@@ -48,6 +48,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(Att
     // ---- prologue: query, codebook, q . g_i ------------------------------------
     float qv[4];
     Elem<DT>::load4(a.q, qrow * kHeadDim + 4 * lane, qv);
+    if (a.lora.x) {                                   // per-user low-rank update of the query row
+        lora_fold_row(a.lora, b, a.T, (int)(qrow % a.T), a.Hq * kHeadDim, hq * kHeadDim + 4 * lane, lane, a.status, qv);
+    }
     if (a.rotate_q) wht128_warp(qv, lane);
     *reinterpret_cast<float4*>(&q_s[wib][4 * lane]) = make_float4(qv[0], qv[1], qv[2], qv[3]);
     {
@@ -347,15 +350,22 @@ static KernelChoice kernel_choice_from_env() {
 // the warp-level kernel once per eight.
 constexpr int64_t kUmmaMinColumns = 80;
 
+// Which tensor-core kernel serves a call, if any (otherwise the lane-per-key kernel does).
+// Measured crossover: the warp-level kernel wins from 128 keys on, and for shorter caches once the lane-per-key
+// kernel would need more than about a thousand warps.
+static void choose_kernels(const AttnArgs& a, bool* use_umma, bool* use_mma) {
+    const KernelChoice choice = kernel_choice_from_env();
+    const int64_t cols = (int64_t)(a.Hq / a.Hkv) * a.T;
+    *use_umma = umma_eligible(a) && (choice == kUmma || (choice == kAuto && cols >= kUmmaMinColumns && a.S >= 128));
+    *use_mma = !*use_umma && mma_eligible(a) &&
+               (choice == kMma || ((choice == kAuto || choice == kUmma) && (a.S >= 128 || a.B * a.Hq * a.T >= 1024)));
+}
+
 static int32_t launch(const AttnArgs& a, cudaStream_t st, size_t ws_bytes) {
     if (a.B == 0 || a.T == 0) return OMNI_OK;
-    const KernelChoice choice = kernel_choice_from_env();
-    // measured crossover: the tensor-core kernel wins from 128 keys on, and for shorter caches once the
-    // lane-per-key kernel would need more than about a thousand warps
-    const int64_t cols = (int64_t)(a.Hq / a.Hkv) * a.T;
-    const bool use_umma = umma_eligible(a) && (choice == kUmma || (choice == kAuto && cols >= kUmmaMinColumns && a.S >= 128));
-    const bool use_mma = !use_umma && mma_eligible(a) &&
-                         (choice == kMma || ((choice == kAuto || choice == kUmma) && (a.S >= 128 || a.B * a.Hq * a.T >= 1024)));
+    bool use_umma, use_mma;
+    choose_kernels(a, &use_umma, &use_mma);
+    OMNI_REQUIRE(!(use_umma && a.lora.x), OMNI_ERR_UNSUPPORTED, "qattn: the tcgen05 kernel takes no folded query update");
     if (use_umma) {
         const int32_t rc = launch_umma(a, st);
         if (rc != OMNI_OK) return rc;
@@ -518,6 +528,29 @@ extern "C" int32_t omni_qattn_decode_lora(const void* q, int32_t q_dtype,
     int32_t st = validate(a, workspace_bytes - (B == 0 || T == 0 ? 0 : qb));
     if (st != OMNI_OK) return st;
     OMNI_REQUIRE(q, OMNI_ERR_ARG, "qattn_decode_lora: NULL q");
+    // The update runs inside the attention kernels' prologues (one launch less, no q_eff round trip) wherever the
+    // kernel that serves the call loads its query rows itself; OMNI_LORA_FOLD=0 keeps the separate launch.
+    // Folded, every work item of a user repeats the down projection, and a lane-per-key warp would repeat it for
+    // one query row each: the fold is taken for the warp-level kernel and small adapters (measured on the reference
+    // benchmark's shape, rank 16 / hidden 128), the separate launch otherwise.  OMNI_LORA_FOLD=1 folds wherever the
+    // serving kernel can, OMNI_LORA_FOLD=0 never.
+    const char* fold_env = getenv("OMNI_LORA_FOLD");
+    bool use_umma = false, use_mma = false;
+    if (B > 0 && T > 0) choose_kernels(a, &use_umma, &use_mma);
+    const bool fold = (fold_env && fold_env[0] == '1') ? !use_umma
+                    : (fold_env && fold_env[0] == '0') ? false
+                    : (use_mma && lora->rank <= 32 && (int64_t)lora->rank * lora->hidden <= 8192);
+    if (fold && B > 0 && T > 0) {
+        OMNI_REQUIRE(lora->hidden > 0 && lora->rank > 0 && lora->n_adapters >= 0, OMNI_ERR_ARG, "qattn_decode_lora: bad extent");
+        OMNI_REQUIRE(lora->rank <= kLoraFoldMaxRank, OMNI_ERR_UNSUPPORTED, "qattn_decode_lora: rank %d exceeds %d", lora->rank, kLoraFoldMaxRank);
+        OMNI_REQUIRE(lora->x && lora->lora_a && lora->lora_b && lora->lora_indices, OMNI_ERR_ARG, "qattn_decode_lora: NULL adapter buffer");
+        a.q = q;
+        a.q_dtype = q_dtype;
+        a.lora = LoraFold{lora->x, lora->lora_a, lora->lora_b, lora->lora_indices, lora->n_adapters, lora->hidden, lora->rank, lora->alpha};
+        st = validate(a, workspace_bytes - qb);
+        if (st != OMNI_OK) return st;
+        return launch(a, (cudaStream_t)stream, workspace_bytes - qb);
+    }
     st = omni_lora_q(q, q_dtype, lora->x, lora->lora_a, lora->lora_b, lora->lora_indices, lora->n_adapters, lora->alpha,
                      B, Hq, T, lora->hidden, lora->rank, q_eff, status_word, stream);
     if (st != OMNI_OK) return st;

@@ -35,7 +35,16 @@
 #include <utility>
 #include <vector>
 
+// This file is compiled twice: as it stands, and (through qattn_mma_lora.cu, which defines OMNI_MMA_LORA as 1) with
+// the per-user query update folded into the prologue.  The second set of kernels is kept apart so that the extra
+// code cannot change the register allocation of the first, whose main loop sits at the register limit.
+#ifndef OMNI_MMA_LORA
+#define OMNI_MMA_LORA 0
+#endif
+
 namespace omni {
+
+constexpr bool kLoraBuild = OMNI_MMA_LORA != 0;
 
 #ifndef OMNI_MMA_WARPS
 #define OMNI_MMA_WARPS 12
@@ -403,7 +412,7 @@ static_assert(kPrepBytesPerUnit == kPrepWords * 4 * 32, "prepared operands: size
 // shared scratch (8 x 128 fp32 query rows, reused for the q.g projections) and `colinfo` the per-column scalars
 // behind it.  Every lane of the warp must call.
 // `inv_lut` = 1 / lut_scale_of(the head's codebook): the score operands carry it, the sign correction does not.
-template <int DT, bool QJL>
+template <int DT, bool QJL, bool LORA>
 __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t b, int hkv, int col0, int ncols, int Gq, float qs,
                                                      float inv_lut, float* qrow, float4* colinfo, int lane, QueryOperands& qo) {
     const int g = lane >> 2, t = lane & 3;
@@ -412,11 +421,18 @@ __device__ __forceinline__ void build_query_operands(const AttnArgs& a, int64_t 
     SignB& sg = qo.sg;
     // ---- prologue: B operands (scaled queries, q.g projections) --------------------------------
     // 1. every column's query row goes to shared memory in fp32 together with its scalars
+    // per-user low-rank update: the up projections of all columns first (left where the rows go next), added below
+    const bool updated = LORA && lora_fold_tile(a.lora, b, a.T, a.Hq, hkv, Gq, col0, ncols, lane, a.status, qrow);
     for (int c = 0; c < ncols; ++c) {
         const int cg = col0 + c;
         const int64_t qrow_idx = (b * a.Hq + (int64_t)hkv * Gq + cg / a.T) * a.T + (cg % a.T);
         float qv[4];
         Elem<DT>::load4(a.q, qrow_idx * kHeadDim + 4 * lane, qv);
+        if (LORA && updated) {
+            const float4 up = *reinterpret_cast<const float4*>(qrow + c * 128 + 4 * lane);   // this lane's own store
+            qv[0] = fmaf(up.x, a.lora.alpha, qv[0]); qv[1] = fmaf(up.y, a.lora.alpha, qv[1]);
+            qv[2] = fmaf(up.z, a.lora.alpha, qv[2]); qv[3] = fmaf(up.w, a.lora.alpha, qv[3]);
+        }
         if (a.rotate_q) wht128_warp(qv, lane);                  // the rotation folded into the query (fp32, not rounded)
         const float amax = warp_max(fmaxf(fmaxf(fabsf(qv[0]), fabsf(qv[1])), fmaxf(fabsf(qv[2]), fabsf(qv[3]))));
         // fp16 operands stay below 2^10 in magnitude; the power of two is re-applied to the scores
@@ -564,7 +580,7 @@ __device__ __forceinline__ void unpack_query_operands(const uint4 (&v)[kPrepWord
 // Preparation launch of split-K calls: one warp per (user, kv head, tile of 8 query columns) builds the item's
 // B operands once and stores them lane by lane; every split of the item then fetches seven 16-byte vectors per
 // lane instead of repeating the projections.
-template <int DT, bool QJL>
+template <int DT, bool QJL, bool LORA>
 __global__ void __launch_bounds__(128) qattn_prep_kernel(AttnArgs a, int64_t n_units) {
     __shared__ __align__(16) unsigned char scratch[4][kWarpScratchBytes];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -579,7 +595,7 @@ __global__ void __launch_bounds__(128) qattn_prep_kernel(AttnArgs a, int64_t n_u
         const int ncols = ncols_all - col0 < 8 ? ncols_all - col0 : 8;
         QueryOperands qo;
         const float inv_lut = 1.f / lut_scale_of(a.codebooks + (a.cb_per_head ? hkv * 16 : 0));
-        build_query_operands<DT, QJL>(a, b, hkv, col0, ncols, Gq, qs, inv_lut, qrow, colinfo, lane, qo);
+        build_query_operands<DT, QJL, LORA>(a, b, hkv, col0, ncols, Gq, qs, inv_lut, qrow, colinfo, lane, qo);
         uint4 v[kPrepWords / 4];
         pack_query_operands(qo, v);
         uint4* dst = reinterpret_cast<uint4*>(a.qprep) + unit * (kPrepWords / 4) * 32 + lane;
@@ -617,7 +633,7 @@ __device__ __forceinline__ void ring_consumed(Ring& r) {
     --r.in_flight;
 }
 
-template <int DT, bool QJL, bool ONECOL, bool VPAIR>
+template <int DT, bool QJL, bool ONECOL, bool VPAIR, bool LORA>
 __global__ void __launch_bounds__(kMmaWarps * 32, 1)
 qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v) {
@@ -745,7 +761,7 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
             for (int k = 0; k < kPrepWords / 4; ++k) v[k] = __ldg(src + 32 * k);
             unpack_query_operands(v, qo);
         } else {
-            build_query_operands<DT, QJL>(a, b, hkv, col0, ncols, Gq, qs, inv_lut, qrow, colinfo, lane, qo);
+            build_query_operands<DT, QJL, LORA>(a, b, hkv, col0, ncols, Gq, qs, inv_lut, qrow, colinfo, lane, qo);
         }
         const uint32_t (&qB)[8][2] = qo.qB;
         const SignB& sg = qo.sg;
@@ -944,6 +960,7 @@ static int32_t encode_nibble_map(CUtensorMap* map, const uint8_t* base) {
     return OMNI_OK;
 }
 
+#if !OMNI_MMA_LORA
 // Self-test of the bounded wait: one warp waits, with the caller's poll limit, on an mbarrier that nothing ever
 // arrives on.  The wait must run out, the warp must report OMNI_ERR_DEVICE_WAIT through the status word exactly
 // like the decode kernel does, and the kernel must return normally (nothing spins unbounded, nothing traps).
@@ -969,6 +986,8 @@ bool mma_eligible(const AttnArgs& a) {
     const int64_t cols = (int64_t)(a.Hq / a.Hkv) * a.T;
     return cols <= 4096 && a.Hkv <= 65535;
 }
+
+#endif  // !OMNI_MMA_LORA
 
 // Per-device facts that never change while the process lives: looked up once, then read without a driver call.
 static int g_sm_count[kMaxDevices];          // 0 = not yet queried
@@ -1034,24 +1053,29 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
         const int64_t units = a.B * a.Hkv * n_ctiles;
         int64_t blocks = (units + 3) / 4;
         if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
-        if (a.with_qjl) qattn_prep_kernel<DT, true><<<(unsigned)blocks, 128, 0, st>>>(a, units);
-        else            qattn_prep_kernel<DT, false><<<(unsigned)blocks, 128, 0, st>>>(a, units);
+        if (a.with_qjl) qattn_prep_kernel<DT, true, kLoraBuild><<<(unsigned)blocks, 128, 0, st>>>(a, units);
+        else            qattn_prep_kernel<DT, false, kLoraBuild><<<(unsigned)blocks, 128, 0, st>>>(a, units);
         rc = check_cuda(cudaGetLastError(), "qattn_prep_kernel launch");
         if (rc != OMNI_OK) return rc;
     }
     const bool one_col = (a.Hq / a.Hkv) * a.T == 1;
     auto kern = a.v_paired
-        ? (a.with_qjl ? (one_col ? qattn_mma_kernel<DT, true, true, true> : qattn_mma_kernel<DT, true, false, true>)
-                      : (one_col ? qattn_mma_kernel<DT, false, true, true> : qattn_mma_kernel<DT, false, false, true>))
-        : (a.with_qjl ? (one_col ? qattn_mma_kernel<DT, true, true, false> : qattn_mma_kernel<DT, true, false, false>)
-                      : (one_col ? qattn_mma_kernel<DT, false, true, false> : qattn_mma_kernel<DT, false, false, false>));
+        ? (a.with_qjl ? (one_col ? qattn_mma_kernel<DT, true, true, true, kLoraBuild> : qattn_mma_kernel<DT, true, false, true, kLoraBuild>)
+                      : (one_col ? qattn_mma_kernel<DT, false, true, true, kLoraBuild> : qattn_mma_kernel<DT, false, false, true, kLoraBuild>))
+        : (a.with_qjl ? (one_col ? qattn_mma_kernel<DT, true, true, false, kLoraBuild> : qattn_mma_kernel<DT, true, false, false, kLoraBuild>)
+                      : (one_col ? qattn_mma_kernel<DT, false, true, false, kLoraBuild> : qattn_mma_kernel<DT, false, false, false, kLoraBuild>));
     rc = allow_full_smem(reinterpret_cast<const void*>(kern), dev);
     if (rc != OMNI_OK) return rc;
     kern<<<grid, kMmaWarps * 32, kMmaSmemBytes, st>>>(a, items, map_k, map_v);
     return check_cuda(cudaGetLastError(), "qattn_mma_kernel launch");
 }
 
+#if OMNI_MMA_LORA
+int32_t launch_mma_lora(const AttnArgs& a, cudaStream_t st) {
+#else
 int32_t launch_mma(const AttnArgs& a, cudaStream_t st) {
+    if (a.lora.x) return launch_mma_lora(a, st);
+#endif
     switch (a.q_dtype) {
         case OMNI_F32:  return launch_mma_t<OMNI_F32>(a, st);
         case OMNI_BF16: return launch_mma_t<OMNI_BF16>(a, st);

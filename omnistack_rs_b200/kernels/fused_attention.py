@@ -20,6 +20,7 @@ from __future__ import annotations
 import ctypes as C
 import functools
 import math
+import weakref
 from typing import Optional
 
 import torch
@@ -127,11 +128,70 @@ def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int, ragged: bool = False
     return best
 
 
-def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
-           seq_lens=None, cache_slots=None, rotate_q=False, unrotate_out=False, n_splits=None, lora=None,
-           v_paired=False):
-    """One call of ``omni_qattn_decode_lora``; ``lora`` = (x, lora_a, lora_b, lora_indices, lora_alpha) or None.
-    ``v_paired``: the V nibble rows are in the pair layout of :func:`pair_v_rows` (a resident cache's own format)."""
+class _DecodeCall:
+    """One ``omni_qattn_decode_lora`` call with everything that stays the same between calls on the same cache
+    already checked and converted: devices, shapes, dtypes, contiguity, the split count, the workspace size and
+    the C arguments of the cache, the codebooks and the flags.  ``run`` supplies what changes per call (the query,
+    the LoRA inputs, the stream, the output)."""
+
+    __slots__ = ("dev", "dev_index", "fn", "q_shape", "q_dtype", "q_code", "mid_args", "ws_bytes", "status_ptr",
+                 "lora_const", "keep", "refs", "ptrs")
+
+    def run(self, q, lora):
+        dev = self.dev
+        if q.device != dev:
+            _lib.require_cuda(q)
+            raise ValueError(f"tensors on different devices: {dev} and {q.device}")
+        if not q.is_contiguous():
+            q = q.contiguous()
+        stream = torch._C._cuda_getCurrentRawStream(self.dev_index) or None
+        ws_ptr = None
+        if self.ws_bytes:
+            ws = _lib.workspace(dev, stream, self.ws_bytes)
+            ws_ptr = ws.data_ptr()
+        lora_arg = None
+        if self.lora_const is not None:
+            la, lb, n_adapters, hidden, rank, alpha = self.lora_const
+            if la is None:                                  # a kept entry: the caller's own (checked) adapter stacks
+                la, lb = lora[1], lora[2]
+            x, idx = lora[0], lora[3]
+            if idx.device.type == "cpu" and idx.numel() and int(idx.max()) >= n_adapters:
+                raise IndexError("lora_indices refers to an adapter that does not exist")
+            x = _lib.as_device(x, dev, torch.float32)
+            idx = _lib.as_device(idx, dev, torch.int32)
+            B, _, T = self.q_shape[:3]
+            if x.shape != (B, T, hidden) or idx.shape != (B,):
+                raise ValueError("LoRA tensors must be x (B,T,hidden), lora_a (n,rank,hidden), lora_b (n,n_heads*128,rank), lora_indices (B,)")
+            lora_arg = C.byref(_lib.OmniLora(x.data_ptr(), la.data_ptr(), lb.data_ptr(), idx.data_ptr(), n_adapters,
+                                             hidden, rank, alpha))
+        out = torch.empty(self.q_shape, dtype=torch.float32, device=dev)
+        with _lib.on_device(dev):
+            _lib.check(self.fn(q.data_ptr(), self.q_code, *self.mid_args, ws_ptr, self.ws_bytes, out.data_ptr(),
+                               self.status_ptr, stream, lora_arg))
+        return out
+
+
+# Prepared calls of the most recent (cache tensors, query shape, flags) combinations.  An entry refers to its tensors
+# weakly and is used only while those very objects are alive and their storage is where it was, so it neither keeps
+# a dropped cache in memory nor survives a recycled ``id``.
+_PLANS: dict = {}
+_MAX_PLANS = 64
+
+
+def clear_prepared_calls() -> None:
+    """Forget the prepared decode calls (they are rebuilt on demand)."""
+    _PLANS.clear()
+
+
+def _plan_key(q, tensors, user_id, scale, flags, n_splits, lora):
+    return (tuple(id(t) for t in tensors), q.shape, q.dtype, user_id if not isinstance(user_id, torch.Tensor) else None,
+            scale, flags, n_splits, None if lora is None else float(lora[4]))
+
+
+def _build_call(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl, seq_lens, cache_slots,
+                rotate_q, unrotate_out, n_splits, lora, v_paired):
+    """Checks and conversions of one decode call; returns the call and whether it may be kept for later calls
+    (only when no argument had to be converted: a converted copy would not follow the caller's tensor)."""
     dev = _lib.require_cuda(q, k_nibbles, k_qjl, k_norms, v_nibbles)
     lib = _lib.ensure_init(dev)
     B, Hq, T, D = q.shape
@@ -144,34 +204,82 @@ def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, w
         raise ValueError(f"cache holds {n_slots} users but q has batch {B}")
     if q.dtype not in _lib.DTYPE_CODE:
         raise TypeError(f"unsupported q dtype {q.dtype}")
-    q = q.contiguous()
+    given = [k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, seq_lens, cache_slots]
     k_nibbles, k_qjl, v_nibbles = k_nibbles.contiguous(), k_qjl.contiguous(), v_nibbles.contiguous()
     k_norms = _lib.as_device(k_norms, dev, torch.float32)
     cb, per_head = _prep_codebooks(codebooks, Hkv, dev)
-    ids, uid = _user_args(user_id, B, dev)
+    if isinstance(user_id, torch.Tensor) and user_id.dtype is torch.int32 and user_id.device == dev and user_id.is_contiguous():
+        if user_id.shape != (B,):
+            raise ValueError(f"user_id tensor must have shape ({B},), got {tuple(user_id.shape)}")
+        ids, uid = user_id, 0
+    else:
+        ids, uid = _user_args(user_id, B, dev)
     lens = None if seq_lens is None else _lib.as_device(seq_lens, dev, torch.int32)
     slots = None if cache_slots is None else _lib.as_device(cache_slots, dev, torch.int32)
+    used = [k_nibbles, k_qjl, k_norms, v_nibbles, cb, ids if isinstance(user_id, torch.Tensor) else user_id, lens, slots]
+    keepable = all(g is u for g, u in zip(given, used))
     if n_splits is None:
         n_splits = _auto_splits(B, Hq, Hkv, T, S, seq_lens is not None)
-    ws, ws_bytes, lora_arg = None, 0, None
+    call = _DecodeCall()
+    call.lora_const = None
+    ws_bytes = 0
     if lora is not None:
         x, la, lb, idx = _prep_lora(q, lora[0], lora[1], lora[2], lora[3], dev)
-        lora_arg = C.byref(_lib.OmniLora(x.data_ptr(), la.data_ptr(), lb.data_ptr(), idx.data_ptr(), la.shape[0],
-                                         la.shape[2], la.shape[1], float(lora[4])))
+        keepable = keepable and la is lora[1] and lb is lora[2]
+        call.lora_const = (la, lb, la.shape[0], la.shape[2], la.shape[1], float(lora[4]))
         ws_bytes = lib.omni_qattn_lora_workspace_bytes(B, Hq, T, n_splits)
     elif n_splits > 1:
         ws_bytes = lib.omni_qattn_workspace_bytes(B, Hq, T, n_splits)
-    stream = _lib.stream_ptr(dev)
-    if ws_bytes:
-        ws = _lib.workspace(dev, stream, ws_bytes)
-    out = torch.empty(B, Hq, T, HEAD_DIM, dtype=torch.float32, device=dev)
-    with _lib.on_device(dev):
-        _lib.check(lib.omni_qattn_decode_lora(
-            _lib.ptr(q), _lib.DTYPE_CODE[q.dtype], _lib.ptr(k_nibbles), _lib.ptr(k_qjl), _lib.ptr(k_norms),
-            _lib.ptr(v_nibbles), _lib.ptr(cb), per_head, _lib.ptr(ids), uid, _lib.ptr(lens), _lib.ptr(slots),
-            B, Hq, Hkv, T, S, Hkv * S, S, float(scale), int(bool(with_qjl)), int(bool(rotate_q)),
-            int(bool(unrotate_out)), int(bool(v_paired)), int(n_splits), _lib.ptr(ws), ws_bytes, _lib.ptr(out), _lib.ptr(_lib.status_word(dev)),
-            stream, lora_arg))
+    call.dev = dev
+    call.dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
+    call.fn = lib.omni_qattn_decode_lora
+    call.q_shape, call.q_dtype, call.q_code = q.shape, q.dtype, _lib.DTYPE_CODE[q.dtype]
+    call.mid_args = (_lib.ptr(k_nibbles), _lib.ptr(k_qjl), _lib.ptr(k_norms), _lib.ptr(v_nibbles), _lib.ptr(cb), per_head,
+                     _lib.ptr(ids), uid, _lib.ptr(lens), _lib.ptr(slots), B, Hq, Hkv, T, S, Hkv * S, S, float(scale),
+                     int(bool(with_qjl)), int(bool(rotate_q)), int(bool(unrotate_out)), int(bool(v_paired)), int(n_splits))
+    call.ws_bytes = ws_bytes
+    call.status_ptr = _lib.ptr(_lib.status_word(dev))
+    call.keep = (k_nibbles, k_qjl, k_norms, v_nibbles, cb, ids, lens, slots)     # alive for the duration of this call
+    return call, keepable
+
+
+def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl,
+           seq_lens=None, cache_slots=None, rotate_q=False, unrotate_out=False, n_splits=None, lora=None,
+           v_paired=False):
+    """One call of ``omni_qattn_decode_lora``; ``lora`` = (x, lora_a, lora_b, lora_indices, lora_alpha) or None.
+    ``v_paired``: the V nibble rows are in the pair layout of :func:`pair_v_rows` (a resident cache's own format).
+    Calls that repeat on the same cache tensors (a serving loop) reuse the checked and converted argument block of
+    the first one; only the query, the LoRA inputs, the stream and the output are handled per call."""
+    tensors = [k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, seq_lens, cache_slots]
+    if isinstance(user_id, torch.Tensor):
+        tensors.append(user_id)
+    if lora is not None:
+        tensors += [lora[1], lora[2]]
+    flags = (bool(with_qjl), bool(rotate_q), bool(unrotate_out), bool(v_paired))
+    key = _plan_key(q, tensors, user_id, scale, flags, n_splits, lora)
+    hit = _PLANS.get(key)
+    if hit is not None:
+        for t, r, p in zip(tensors, hit.refs, hit.ptrs):
+            if t is None:
+                if r is not None:
+                    break
+            elif r is None or r() is not t or t.data_ptr() != p:
+                break
+        else:
+            return hit.run(q, lora)
+        del _PLANS[key]
+    call, keepable = _build_call(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl, seq_lens,
+                                 cache_slots, rotate_q, unrotate_out, n_splits, lora, v_paired)
+    out = call.run(q, lora)
+    if keepable:
+        call.refs = tuple(None if t is None else weakref.ref(t) for t in tensors)
+        call.ptrs = tuple(None if t is None else t.data_ptr() for t in tensors)
+        call.keep = None                                    # the entry must not keep the caller's cache alive
+        if call.lora_const is not None:                     # nor the adapter stacks: re-read through the weak references
+            call.lora_const = (None, None) + call.lora_const[2:]
+        if len(_PLANS) >= _MAX_PLANS:
+            del _PLANS[next(iter(_PLANS))]
+        _PLANS[key] = call
     return out
 
 

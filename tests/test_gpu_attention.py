@@ -260,6 +260,97 @@ def test_lora_prologue_shapes_and_batch_consistency(dev):
     assert torch.equal(bad, plain)                        # such rows keep q unchanged
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,T,S,hid,rank", [
+    (64, 32, 8, 1, 50, 128, 16),      # the reference benchmark's shape: warp-level kernel, the unrolled small case
+    (9, 24, 8, 1, 140, 128, 32),      # the unrolled small case with three columns per kv head (odd tail) and rank 32
+    (5, 8, 1, 1, 260, 128, 8),        # ... eight columns, rank 8
+    (4, 8, 2, 1, 150, 384, 12),       # general code, vector loads
+    (3, 8, 2, 1, 40, 100, 6),         # lane-per-key kernel, scalar loads
+    (2, 4, 2, 3, 200, 256, 40),       # several tokens per user, more adapter rows than lanes
+    (33, 8, 8, 1, 130, 64, 128),      # one query column per kv head, the largest rank
+])
+def test_lora_update_inside_the_attention_kernels(dev, B, Hq, Hkv, T, S, hid, rank, monkeypatch):
+    """The per-user query update runs in the attention kernels' prologues (reference kernels/fused_attention.py:166-191
+    does the same in its kernel).  Checked against the oracle and, bit for bit, against the separate update launch
+    followed by the same attention kernel."""
+    fa = attn_mod()
+    from omnistack_rs_b200 import _lib
+    kn, kq, kr, vn, cb, gen = make_cache(B, Hkv, S, seed=B + rank, user_id=6)
+    q = torch.randn(B, Hq, T, 128, generator=gen).to(torch.bfloat16)
+    x = torch.randn(B, T, hid, generator=gen)
+    la = torch.randn(5, rank, hid, generator=gen) * (0.5 / hid ** 0.5)
+    lb = torch.randn(5, Hq * 128, rank, generator=gen) * (0.5 / rank ** 0.5)
+    idx = torch.randint(-1, 5, (B,), generator=gen, dtype=torch.int32)
+    idx[0] = -1
+    idx[B - 1] = 4
+    want = orc.decode_attention(orc.apply_lora_to_q(q, x, la, lb, idx, 0.3), kn, kq, kr, vn, cb, 6)
+    cache = to_dev(dev, kn, kq, kr, vn, cb)
+    lora = dict(x=x.to(dev), lora_a=la.to(dev), lora_b=lb.to(dev), lora_indices=idx.to(dev), lora_alpha=0.3)
+    for ns in (1, 2):
+        monkeypatch.setenv("OMNI_LORA_FOLD", "1")
+        folded = fa.omni_attn(q.to(dev), *cache, user_id=6, n_splits=ns, **lora)
+        monkeypatch.setenv("OMNI_LORA_FOLD", "0")
+        separate = fa.omni_attn(q.to(dev), *cache, user_id=6, n_splits=ns, **lora)
+        monkeypatch.delenv("OMNI_LORA_FOLD", raising=False)                # the library's own choice between the two
+        chosen = fa.omni_attn(q.to(dev), *cache, user_id=6, n_splits=ns, **lora)
+        assert (folded.cpu() - want).abs().max() <= ATOL, ns
+        assert torch.equal(folded, separate) and torch.equal(chosen, separate), ns
+    monkeypatch.delenv("OMNI_LORA_FOLD", raising=False)
+    base = fa.omni_attn(q.to(dev), *cache, user_id=6)
+    assert torch.equal(fa.omni_attn(q.to(dev), *cache, user_id=6, **lora)[0], base[0])          # index -1
+    lora["lora_indices"] = torch.full((B,), 5, dtype=torch.int32, device=dev)                   # one past the last adapter
+    with pytest.raises(IndexError):
+        bad = fa.omni_attn(q.to(dev), *cache, user_id=6, **lora)
+        _lib.check_device_status(dev)
+    assert torch.equal(bad, base)
+
+
+def test_prepared_calls_follow_their_tensors(dev):
+    """Repeated calls on the same cache tensors reuse a prepared argument block.  It must see in-place changes of
+    the cache and of per-user lengths, must not be used for other tensors, and must not keep a dropped cache alive."""
+    import gc, weakref
+    fa = attn_mod()
+    fa.clear_prepared_calls()
+    kn, kq, kr, vn, cb, gen = make_cache(3, 2, 200, seed=61, user_id=2)
+    q = torch.randn(3, 4, 1, 128, generator=gen).to(torch.bfloat16)
+    cache = list(to_dev(dev, kn, kq, kr, vn, cb))
+    qd = q.to(dev)
+    first = fa.omni_attn(qd, *cache, user_id=2)
+    assert len(fa._PLANS) == 1
+    assert torch.equal(fa.omni_attn(qd, *cache, user_id=2), first)
+    assert (first.cpu() - orc.decode_attention(q, kn, kq, kr, vn, cb, 2)).abs().max() <= ATOL
+    # in-place change of the cache: same tensors, new contents
+    kn2, kq2, kr2, vn2, _, _ = make_cache(3, 2, 200, seed=62, user_id=2)
+    for t_dev, t_new in zip(cache[:4], (kn2, kq2, kr2, vn2)):
+        t_dev.copy_(t_new)
+    second = fa.omni_attn(qd, *cache, user_id=2)
+    assert (second.cpu() - orc.decode_attention(q, kn2, kq2, kr2, vn2, cb, 2)).abs().max() <= ATOL
+    # lengths on the device are read by the kernel at launch; lengths on the host are converted per call
+    lens_dev = torch.tensor([200, 100, 7], dtype=torch.int32, device=dev)
+    lens_cpu = torch.tensor([200, 100, 7], dtype=torch.int64)
+    a = fa.omni_attn(qd, *cache, user_id=2, seq_lens=lens_dev)
+    b = fa.omni_attn(qd, *cache, user_id=2, seq_lens=lens_cpu)
+    assert torch.equal(a, b)
+    lens_dev[1] = 33
+    lens_cpu[1] = 33
+    a2 = fa.omni_attn(qd, *cache, user_id=2, seq_lens=lens_dev)
+    b2 = fa.omni_attn(qd, *cache, user_id=2, seq_lens=lens_cpu)
+    assert torch.equal(a2, b2) and not torch.equal(a2[1], a[1]) and torch.equal(a2[0], a[0])
+    want = orc.decode_attention(q[1:2], kn2[1:2, :, :33], kq2[1:2, :, :33], kr2[1:2, :, :33], vn2[1:2, :, :33], cb, 2)
+    assert (a2[1:2].cpu() - want).abs().max() <= ATOL
+    # other tensors of the same shape get their own call; a dropped cache is released
+    other = list(to_dev(dev, kn, kq, kr, vn, cb))
+    assert torch.equal(fa.omni_attn(qd, *other, user_id=2), first)
+    probe = weakref.ref(other[0])
+    del other
+    gc.collect()
+    assert probe() is None
+    # a query on another dtype or shape is not served by the kept call
+    assert (fa.omni_attn(qd.float(), *cache, user_id=2) - second).abs().max() <= 1e-6
+    with pytest.raises(ValueError):
+        fa.omni_attn(qd[:2], *cache, user_id=2)
+
+
 @pytest.mark.parametrize("n_splits", [16, 37, 200, None])
 def test_single_user_long_cache_many_splits(dev, n_splits):
     """One user, 32 q / 8 kv heads, 6,000 keys: far more key splits than resident warps need, odd split counts,
