@@ -381,8 +381,16 @@ static int32_t launch(const AttnArgs& a, cudaStream_t st, size_t ws_bytes) {
             // a call whose items all run at once would only see the extra launch on its critical path (latency).
             const int64_t n_items = a.B * a.Hkv * (((int64_t)(a.Hq / a.Hkv) * a.T + 7) / 8) * a.n_splits;
             const bool many = n_items >= 2 * 148 * 12 || (prep_env && prep_env[0] == '1');
-            if (many && !(prep_env && prep_env[0] == '0') && ws_bytes >= omni_qattn_workspace_bytes(a.B, a.Hq, a.T, a.n_splits))
-                m.qprep = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(a.ws + partial_floats) + kWorkCounterBytes);
+            if (many && !(prep_env && prep_env[0] == '0') && ws_bytes >= omni_qattn_workspace_bytes(a.B, a.Hq, a.T, a.n_splits)) {
+                char* behind = reinterpret_cast<char*>(a.ws + partial_floats) + kWorkCounterBytes;
+                m.qprep = reinterpret_cast<uint32_t*>(behind + user_order_bytes(a.B));
+                // users of different lengths: the preparation launch also sorts them, longest first
+                // (OMNI_QATTN_ORDER=0 keeps index order: tests and profiling)
+                const char* order_env = getenv("OMNI_QATTN_ORDER");
+                const bool one_col = (int64_t)(a.Hq / a.Hkv) * a.T == 1;          // those kernel variants keep index order
+                if (a.seq_lens && !one_col && a.B > 1 && a.B <= kMaxOrderedUsers && !(order_env && order_env[0] == '0'))
+                    m.user_order = reinterpret_cast<int2*>(behind);
+            }
         }
         const int32_t rc = launch_mma(m, st);
         if (rc != OMNI_OK) return rc;
@@ -467,9 +475,10 @@ using namespace omni;
 
 extern "C" size_t omni_qattn_workspace_bytes(int64_t B, int32_t Hq, int32_t T, int32_t n_splits) {
     if (n_splits <= 1 || B <= 0 || Hq <= 0 || T <= 0) return 0;
-    // partial states, ticket counters, and room for the prepared query operands of every (user, kv head, tile of 8
+    // partial states, ticket counters, the users' processing order, and room for the prepared query operands of every (user, kv head, tile of 8
     // query columns): at most Hq * ceil((T + 7) / 8) such tiles per user whatever the head grouping
-    return partials_and_counter_bytes(B, Hq, T, n_splits) + (size_t)B * Hq * ((T + 7 + 7) / 8) * kPrepBytesPerUnit;
+    return partials_and_counter_bytes(B, Hq, T, n_splits) + user_order_bytes(B) +
+           (size_t)B * Hq * ((T + 7 + 7) / 8) * kPrepBytesPerUnit;
 }
 
 extern "C" int32_t omni_qattn_decode(const void* q, int32_t q_dtype,

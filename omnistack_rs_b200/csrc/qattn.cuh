@@ -38,6 +38,10 @@ struct AttnArgs {
     int only_if_wide;          // lane-per-key kernel: 1 = run only when the codebooks are outside the fp16 table's
                                // range (it then completes a call whose tensor-core launch stood down), 0 = always
     LoraFold lora;             // query update folded into the prologue (warp-level and lane-per-key kernels)
+    int2* user_order;          // warp-level kernel, split-K calls with per-user lengths: (user, clamped length) pairs with
+                               // the longest caches first, written by the preparation launch; work items are numbered in
+                               // this order, so the tickets hand out the long items first and the short ones fill the
+                               // end of the launch (null: users in index order)
 };
 
 // The tensor-core kernel dequantises through a table of fp16 centroid pairs.  fp16 rounds a centroid by at most
@@ -63,6 +67,9 @@ __device__ __forceinline__ float lut_scale_of(const float* cb) {
 
 constexpr int kWsStride = 132;     // floats per split-K partial: 128 accumulators, max, sum, 2 pad
 constexpr size_t kWorkCounterBytes = 4096;   // kSeeds (the most kv heads a call may have) 32-bit counters
+// Split-K workspace: partial states | ticket counters (kWorkCounterBytes) | user order | prepared query operands.
+constexpr int64_t kMaxOrderedUsers = 16384;          // one CTA sorts them in the preparation launch
+inline size_t user_order_bytes(int64_t B) { return B <= kMaxOrderedUsers ? (((size_t)B * 8) + 255) & ~(size_t)255 : 0; }
 constexpr size_t kPrepBytesPerUnit = 32 * 4 * 32;   // prepared query operands of one work item: 32 words per lane
 
 __device__ __forceinline__ float warp_max(float v) {

@@ -580,15 +580,60 @@ __device__ __forceinline__ void unpack_query_operands(const uint4 (&v)[kPrepWord
 // Preparation launch of split-K calls: one warp per (user, kv head, tile of 8 query columns) builds the item's
 // B operands once and stores them lane by lane; every split of the item then fetches seven 16-byte vectors per
 // lane instead of repeating the projections.
+// Users in order of decreasing cache length, as (user, clamped length) pairs: a counting sort over 1,024 length
+// classes by one CTA of 128 threads (the order inside a class is whatever the atomics make it: it only decides
+// which warp serves which work item, never a result).  The ticket scheduler hands items out in this order, so the
+// long ones start first and the short ones even out the end of the launch.
+static __device__ void sort_users_by_length(const AttnArgs& a) {
+    __shared__ int hist[1024];
+    __shared__ int warp_sum_s[4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < 1024; i += 128) hist[i] = 0;
+    __syncthreads();
+    const int64_t S = a.S > 0 ? a.S : 1;
+    for (int64_t b = tid; b < a.B; b += 128) {
+        int64_t len = a.seq_lens[b];
+        len = len < 0 ? 0 : (len > a.S ? a.S : len);
+        atomicAdd(&hist[1023 - (int)(len * 1023 / S)], 1);
+    }
+    __syncthreads();
+    int mine[8], sum = 0;                               // thread t owns classes 8t .. 8t+7
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { mine[k] = hist[8 * tid + k]; sum += mine[k]; }
+    int incl = sum;
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+        const int o = __shfl_up_sync(kFullMask, incl, m);
+        if (lane >= m) incl += o;
+    }
+    if (lane == 31) warp_sum_s[warp] = incl;
+    __syncthreads();
+    int start = incl - sum;
+    for (int w = 0; w < warp; ++w) start += warp_sum_s[w];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { hist[8 * tid + k] = start; start += mine[k]; }
+    __syncthreads();
+    for (int64_t b = tid; b < a.B; b += 128) {
+        int64_t len = a.seq_lens[b];
+        len = len < 0 ? 0 : (len > a.S ? a.S : len);
+        const int pos = atomicAdd(&hist[1023 - (int)(len * 1023 / S)], 1);
+        a.user_order[pos] = make_int2((int)b, (int)len);
+    }
+}
+
 template <int DT, bool QJL, bool LORA>
-__global__ void __launch_bounds__(128) qattn_prep_kernel(AttnArgs a, int64_t n_units) {
+__global__ void __launch_bounds__(128) qattn_prep_kernel(AttnArgs a, int64_t n_units, unsigned n_unit_blocks) {
     __shared__ __align__(16) unsigned char scratch[4][kWarpScratchBytes];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (blockIdx.x == n_unit_blocks) {                 // the extra CTA of a call with per-user lengths
+        sort_users_by_length(a);
+        return;
+    }
     const int Gq = a.Hq / a.Hkv, ncols_all = Gq * a.T, n_ctiles = (ncols_all + 7) / 8;
     const float qs = a.scale * kLog2e;
     float* qrow = reinterpret_cast<float*>(scratch[warp]);
     float4* colinfo = reinterpret_cast<float4*>(qrow + 8 * 128);
-    for (int64_t unit = (int64_t)blockIdx.x * 4 + warp; unit < n_units; unit += (int64_t)gridDim.x * 4) {
+    for (int64_t unit = (int64_t)blockIdx.x * 4 + warp; unit < n_units; unit += (int64_t)n_unit_blocks * 4) {
         const int col0 = 8 * (int)(unit % n_ctiles);
         const int hkv = (int)((unit / n_ctiles) % a.Hkv);
         const int64_t b = unit / n_ctiles / a.Hkv;
@@ -717,11 +762,19 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         int hkv = cb_head;
         if (head_in_item) { hkv = (int)(rest % a.Hkv); rest /= a.Hkv; }
         const int split = (int)(rest % a.n_splits);
-        const int64_t b = rest / a.n_splits;
+        int64_t b = rest / a.n_splits;
 
         // ---- key range of this split; start the first copies before the prologue ------------------
-        int64_t len = a.seq_lens ? (int64_t)a.seq_lens[b] : a.S;
-        len = len < 0 ? 0 : (len > a.S ? a.S : len);
+        int64_t len;
+        if (!ONECOL && a.user_order) {                  // items are numbered by decreasing cache length (not in the
+                                                        // one-column variants, which have no register to spare)
+            const int2 e = __ldg(a.user_order + b);
+            b = e.x;
+            len = e.y;
+        } else {
+            len = a.seq_lens ? (int64_t)a.seq_lens[b] : a.S;
+            len = len < 0 ? 0 : (len > a.S ? a.S : len);
+        }
         int64_t per = (len + a.n_splits - 1) / a.n_splits;
         per = (per + 31) / 32 * 32;
         const int64_t s0 = (int64_t)split * per;
@@ -1053,12 +1106,14 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
         const int64_t units = a.B * a.Hkv * n_ctiles;
         int64_t blocks = (units + 3) / 4;
         if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
-        if (a.with_qjl) qattn_prep_kernel<DT, true, kLoraBuild><<<(unsigned)blocks, 128, 0, st>>>(a, units);
-        else            qattn_prep_kernel<DT, false, kLoraBuild><<<(unsigned)blocks, 128, 0, st>>>(a, units);
+        const unsigned grid_prep = (unsigned)blocks + (a.user_order ? 1u : 0u);     // one more CTA sorts the users by length
+        if (a.with_qjl) qattn_prep_kernel<DT, true, kLoraBuild><<<grid_prep, 128, 0, st>>>(a, units, (unsigned)blocks);
+        else            qattn_prep_kernel<DT, false, kLoraBuild><<<grid_prep, 128, 0, st>>>(a, units, (unsigned)blocks);
         rc = check_cuda(cudaGetLastError(), "qattn_prep_kernel launch");
         if (rc != OMNI_OK) return rc;
     }
     const bool one_col = (a.Hq / a.Hkv) * a.T == 1;
+    if (one_col && a.user_order) return set_error(OMNI_ERR_ARG, "qattn: the one-column kernels take the users in index order");
     auto kern = a.v_paired
         ? (a.with_qjl ? (one_col ? qattn_mma_kernel<DT, true, true, true, kLoraBuild> : qattn_mma_kernel<DT, true, false, true, kLoraBuild>)
                       : (one_col ? qattn_mma_kernel<DT, false, true, true, kLoraBuild> : qattn_mma_kernel<DT, false, false, true, kLoraBuild>))

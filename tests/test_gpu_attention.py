@@ -351,6 +351,37 @@ def test_prepared_calls_follow_their_tensors(dev):
         fa.omni_attn(qd[:2], *cache, user_id=2)
 
 
+@pytest.mark.parametrize("per_head", [False, True])
+def test_longest_first_order_of_ragged_users(dev, per_head, monkeypatch):
+    """Split-K calls with per-user lengths number their work items by decreasing cache length (sorted in the
+    preparation launch), so that the tickets hand out the long items first.  The order only decides which warp
+    serves which item: the rows equal those of the index order bit for bit, with cache slots, empty users and
+    per-head codebooks as well."""
+    fa = attn_mod()
+    B, Hq, Hkv, S = 37, 8, 2, 420
+    kn, kq, kr, vn, cb, gen = make_cache(B + 5, Hkv, S, seed=23, user_id=3, per_head=per_head)
+    q = torch.randn(B, Hq, 1, 128, generator=gen).to(torch.bfloat16)
+    lens = torch.randint(0, S + 1, (B,), generator=gen, dtype=torch.int32)
+    lens[3] = 0
+    lens[11] = S
+    slots = torch.randperm(B + 5, generator=gen)[:B].to(torch.int32)
+    args = to_dev(dev, q, kn, kq, kr, vn, cb)
+    monkeypatch.setenv("OMNI_QATTN_PREP", "1")
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("OMNI_QATTN_ORDER", flag)
+        outs[flag] = fa.omni_attn(*args, user_id=3, n_splits=3, seq_lens=lens.to(dev), cache_slots=slots.to(dev))
+    assert torch.equal(outs["1"], outs["0"])
+    for b in (0, 3, 11, 36):
+        n, sl = int(lens[b]), int(slots[b])
+        if n == 0:
+            assert float(outs["1"][b].abs().max()) == 0.0
+            continue
+        want = orc.decode_attention(q[b:b + 1], kn[sl:sl + 1, :, :n], kq[sl:sl + 1, :, :n], kr[sl:sl + 1, :, :n],
+                                    vn[sl:sl + 1, :, :n], cb, 3)
+        assert (outs["1"][b:b + 1].cpu() - want).abs().max() <= ATOL
+
+
 @pytest.mark.parametrize("n_splits", [16, 37, 200, None])
 def test_single_user_long_cache_many_splits(dev, n_splits):
     """One user, 32 q / 8 kv heads, 6,000 keys: far more key splits than resident warps need, odd split counts,
@@ -415,6 +446,9 @@ def test_wide_codebook_with_peaked_softmax(dev, kernel_choice):
     want = orc.decode_attention(qq, kn, kq, kr, vn, cb, 3)
     assert float(want.abs().max()) > 5.0
     got = fa.omni_attn(*to_dev(dev, qq, kn, kq, kr, vn, cb), user_id=3)
+    assert (got.cpu() - want).abs().max() <= ATOL
+    # split-K: the tensor-core launch stands down, the fp32 kernel writes the partial states the combine launch merges
+    got = fa.omni_attn(*to_dev(dev, qq, kn, kq, kr, vn, cb), user_id=3, n_splits=4)
     assert (got.cpu() - want).abs().max() <= ATOL
 
 
