@@ -99,8 +99,9 @@ def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int, ragged: bool = False
     for every swept shape): a work unit of the tensor-core kernel - one (user, kv head, tile of 8 query columns,
     split) - costs about 3 us plus 22 ns per key when it has an SM to itself, rising to 45 ns per key with
     twelve warps per SM; units run in rounds of 148 x 12; the merge costs 2 us plus its bytes at 1 TB/s.
-    ``ragged`` (per-user cache lengths were given): at least 8 splits of 512 keys or more, so that the ticket
-    scheduling can even the lengths out, unless every warp has many units anyway."""
+    ``ragged`` (per-user cache lengths were given): at least 8 splits of 512 keys or more (4 where the library
+    orders the users by length), so that the ticket scheduling can even the lengths out, unless every warp has many
+    units anyway."""
     if S < 128 and B * Hq * T < 1024:
         return 1                                   # the lane-per-key kernel's shapes
     units = max(1, B * Hkv * -(-((Hq // Hkv) * T) // 8))
@@ -124,7 +125,11 @@ def _auto_splits(B: int, Hq: int, Hkv: int, T: int, S: int, ragged: bool = False
     if best_cost >= 0.8 * unsplit_cost:
         best = 1
     if ragged and units < 8 * _WARP_SLOTS:
-        best = max(best, min(8, S // 512))
+        # calls the library serves longest user first (several query columns per kv head, enough work items for its
+        # preparation launch, at most 16,384 users) balance with coarser splits: measured on configuration 2,
+        # 0.310-0.312 ms with 3 to 6 splits against 0.317 with 8
+        ordered = 1 < B <= 16384 and (Hq // Hkv) * T > 1 and units * 4 >= 2 * _WARP_SLOTS
+        best = max(best, min(4 if ordered else 8, S // 512))
     return best
 
 
