@@ -717,8 +717,7 @@ qattn_mma_kernel(AttnArgs a, int64_t n_items, const __grid_constant__ CUtensorMa
         }
     }
     const uint32_t lut_lane = smem_base + lut_off + 4 * lane;                  // bits 8..15 are zero
-    float* qrow = reinterpret_cast<float*>(smem + my_off + kStages * kStageBytes);   // [8][128] fp32 query rows ...
-    float* qg_s = qrow;                                                               // ... later [8][64] q.g projections
+    float* qrow = reinterpret_cast<float*>(smem + my_off + kStages * kStageBytes);   // [8][128] fp32 query rows, later [8][64] q.g projections
     float4* colinfo = reinterpret_cast<float4*>(qrow + 8 * 128);                      // per column: f, post, q.g scale, -
     Ring ring;
     ring.stage0 = smem_base + my_off;
