@@ -286,7 +286,7 @@ static __device__ __noinline__ bool lora_fold_tile(const LoraFold L, int64_t b, 
 bool mma_eligible(const AttnArgs& a);
 int32_t launch_mma(const AttnArgs& a, cudaStream_t st);
 int32_t launch_mma_lora(const AttnArgs& a, cudaStream_t st);   // qattn_mma_lora.cu: the same kernels with a.lora applied
-// tcgen05 kernel (qattn_umma.cu): kv heads with many query columns, V rows in the reference layout.
+// tcgen05 kernel (qattn_umma.cu): kv heads with many query columns.
 bool umma_eligible(const AttnArgs& a);
 int32_t launch_umma(const AttnArgs& a, cudaStream_t st);
 // One-warp kernel that lets a bounded mbarrier wait run out on purpose (nothing arrives on its barrier).

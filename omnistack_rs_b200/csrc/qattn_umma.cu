@@ -21,8 +21,8 @@
 // ((8 rows x 16 B) core matrices, LBO between the two K chunks of an instruction, SBO between row groups) and
 // MN-major (8 K-rows x 16 B core matrices, SBO between MN chunks, LBO between K groups).
 //
-// Covers: V rows in the reference layout (a pair-layout cache stays with the warp-level kernel), any S, ragged
-// lengths, cache slots, split-K (static assignment), rotation folding.  Wide codebooks (a centroid of magnitude 8 or
+// Covers: V rows in the reference or the pair layout, any S, ragged lengths, cache slots, split-K (static
+// assignment), rotation folding.  Wide codebooks (a centroid of magnitude 8 or
 // more) make the grid stand down exactly like the warp-level kernel; the fp32 kernel launched behind it takes over.
 #include "qattn.cuh"
 #include <mutex>
@@ -253,6 +253,7 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
         const int64_t slot = a.cache_slots ? (int64_t)a.cache_slots[b] : b;
         const int64_t row0 = slot * a.ks_b + (int64_t)hkv * a.ks_h + s0;
         const int nkeys = s1 > s0 ? (int)(s1 - s0) : 0;
+        const int64_t paired_limit = (len & ~(int64_t)7) - s0;      // pair layout: key offsets of this split below this
         const bool col_on = tid < ncols;
         const int cg = col0 + (col_on ? tid : 0);
         const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + cg / a.T) * a.T + (cg % a.T);
@@ -398,12 +399,35 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
                 tc_fence_after();
             }
             const uint32_t rowv = sV + (uint32_t)(tid & 7) * 16 + (uint32_t)(tid >> 3) * kUVLbo;
+            // Pair layout of V (groups of eight keys that lie completely below the user's length): the row of a pair's
+            // first key holds the even-d nibbles of both keys, the row of the second key the odd-d ones, so a table
+            // lookup yields (first key, second key) at one dim.  The two threads of a pair (lanes l and l ^ 3) exchange
+            // their lookups and each keeps its own key's halves: (own low, other low) for the first key, (other high,
+            // own high) for the second.  A group is paired as a whole, and groups coincide with runs of eight lanes.
+            const bool v_pair = a.v_paired && (int64_t)(k0 + tid) < paired_limit;
+            if (__ballot_sync(0xffffffffu, v_pair) != 0u) {
+                const uint32_t sel = v_pair ? ((tid & 2) ? 0x3276u : 0x5410u) : 0x3210u;
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-                u_dequant_store(rowv + (uint32_t)(4 * c4 + 0) * kUVSbo, lut_lane, vw[c4].x);
-                u_dequant_store(rowv + (uint32_t)(4 * c4 + 1) * kUVSbo, lut_lane, vw[c4].y);
-                u_dequant_store(rowv + (uint32_t)(4 * c4 + 2) * kUVSbo, lut_lane, vw[c4].z);
-                u_dequant_store(rowv + (uint32_t)(4 * c4 + 3) * kUVSbo, lut_lane, vw[c4].w);
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    const uint32_t ws[4] = {vw[c4].x, vw[c4].y, vw[c4].z, vw[c4].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t l0 = u_lut<0>(lut_lane, ws[e]), l1 = u_lut<1>(lut_lane, ws[e]);
+                        const uint32_t l2 = u_lut<2>(lut_lane, ws[e]), l3 = u_lut<3>(lut_lane, ws[e]);
+                        const uint32_t o0 = __shfl_xor_sync(0xffffffffu, l0, 3), o1 = __shfl_xor_sync(0xffffffffu, l1, 3);
+                        const uint32_t o2 = __shfl_xor_sync(0xffffffffu, l2, 3), o3 = __shfl_xor_sync(0xffffffffu, l3, 3);
+                        u_sts16(rowv + (uint32_t)(4 * c4 + e) * kUVSbo, __byte_perm(l0, o0, sel), __byte_perm(l1, o1, sel),
+                                __byte_perm(l2, o2, sel), __byte_perm(l3, o3, sel));
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 0) * kUVSbo, lut_lane, vw[c4].x);
+                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 1) * kUVSbo, lut_lane, vw[c4].y);
+                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 2) * kUVSbo, lut_lane, vw[c4].z);
+                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 3) * kUVSbo, lut_lane, vw[c4].w);
+                }
             }
             if (k0 + kUThreads < nkeys) fetch_tile(k0 + kUThreads);      // in flight during the products and the softmax
             u_fence_async_smem();
@@ -582,7 +606,7 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
 // ---- host side ---------------------------------------------------------------------------------------------
 bool umma_eligible(const AttnArgs& a) {
     const int64_t cols = (int64_t)(a.Hq / a.Hkv) * a.T;
-    return !a.v_paired && cols >= 1 && cols <= 4096 && a.Hkv <= 65535;
+    return cols >= 1 && cols <= 4096 && a.Hkv <= 65535;
 }
 
 template <int DT>

@@ -79,3 +79,25 @@ def test_umma_is_the_default_for_many_columns(dev, monkeypatch):
     tiles = fa.omni_attn(*d, user_id=6)
     want = orc.decode_attention(q, kn, kq, kr, vn, cb, 6)
     assert (auto.cpu() - want).abs().max() <= ATOL and (tiles.cpu() - want).abs().max() <= ATOL
+
+
+@pytest.mark.parametrize("S", [1, 7, 8, 9, 127, 128, 129, 136, 250, 700])
+def test_umma_reads_the_pair_layout_of_v(dev, S):
+    """V rows in a resident cache's pair layout: the two threads of a key pair exchange their table lookups, the
+    user's last incomplete group of eight stays in the reference layout.  Same bits as the reference-layout call,
+    with ragged lengths, splits and several query tokens."""
+    fa = attn_mod()
+    kn, kq, kr, vn, cb, gen = make_cache(3, 2, S, seed=2000 + S, user_id=4)
+    q = torch.randn(3, 8, 5, 128, generator=gen).to(torch.bfloat16)
+    lens = torch.tensor([S, max(1, S // 2), max(1, S - 3)], dtype=torch.int64)
+    d = to_dev(dev, q, kn, kq, kr, vn, cb)
+    paired = d[4].clone()
+    fa.pair_v_rows(paired, 0, lens.to(dev))
+    for ns in (1, 3):
+        ref = fa.omni_attn(*d, user_id=4, seq_lens=lens.to(dev), n_splits=ns)
+        got = fa.omni_attn(d[0], d[1], d[2], d[3], paired, d[5], user_id=4, seq_lens=lens.to(dev), n_splits=ns, v_paired=True)
+        assert torch.equal(got, ref), (S, ns)
+    for b in range(3):
+        n = int(lens[b])
+        want = orc.decode_attention(q[b:b + 1], kn[b:b + 1, :, :n], kq[b:b + 1, :, :n], kr[b:b + 1, :, :n], vn[b:b + 1, :, :n], cb, 4)
+        assert (got[b:b + 1].cpu() - want).abs().max() <= ATOL
