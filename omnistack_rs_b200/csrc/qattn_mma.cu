@@ -629,6 +629,8 @@ __global__ void __launch_bounds__(128) qattn_prep_kernel(AttnArgs a, int64_t n_u
         sort_users_by_length(a);
         return;
     }
+    if (blockIdx.x == 0 && a.work_counter)             // the attention launch behind this one starts from zeroed tickets
+        for (int i = threadIdx.x; i < (int)(kWorkCounterBytes / 4); i += blockDim.x) a.work_counter[i] = 0u;
     const int Gq = a.Hq / a.Hkv, ncols_all = Gq * a.T, n_ctiles = (ncols_all + 7) / 8;
     const float qs = a.scale * kLog2e;
     float* qrow = reinterpret_cast<float*>(scratch[warp]);
@@ -1080,7 +1082,8 @@ static int32_t launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     int64_t items, ctas;
     unsigned gy;
     const int64_t n_ctiles = ((int64_t)(a.Hq / a.Hkv) * a.T + 7) / 8;
-    if (a.work_counter) OMNI_CUDA(cudaMemsetAsync(a.work_counter, 0, kWorkCounterBytes, st));
+    // ticket counters: cleared by the preparation launch when there is one, by a memset node otherwise
+    if (a.work_counter && !a.qprep) OMNI_CUDA(cudaMemsetAsync(a.work_counter, 0, kWorkCounterBytes, st));
     if (a.cb_per_head) {
         items = a.B * a.n_splits * n_ctiles;
         ctas = sms / a.Hkv > 0 ? sms / a.Hkv : 1;
