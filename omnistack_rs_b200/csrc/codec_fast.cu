@@ -27,12 +27,13 @@ namespace omni {
 constexpr int kFqWarps = 8;
 constexpr int kFqMaxHeads = 32;
 
-// Per-head quantiser tables in shared memory.
-struct HeadTables {
+// Per-head quantiser tables in shared memory.  The cell records come first and the struct is 256-byte aligned, so
+// that (byte offset of a cell) | (address of the table) addresses a record without an add.
+struct alignas(256) HeadTables {
+    float2 cell2[32];       // per grid cell: x = threshold between the cell's two codes, y = the lower code (int bits)
     float thr[20];          // thr[c], c = 1..15: smallest fp32 y whose code is >= c; thr[16] = +inf
     float cb[16];
-    float2 cell2[32];       // per grid cell: x = threshold between the cell's two codes, y = the lower code (int bits)
-    float inv32, off32;     // cell(y) = rn(31 * sat(y * inv32 + off32))
+    float inv32, off32;     // cell(y): see cell_offset
     float guard;            // |y| <= guard: the threshold shortcut is valid
     int valid;              // 0: this codebook always takes the defining scan; 1: grid cell + one compare;
                             // 2: binary search over the 15 exact thresholds (the grid cannot resolve them)
@@ -57,10 +58,14 @@ __device__ __forceinline__ int code_by_scan(float y, const float* cb) {
     }
     return code;
 }
-__device__ __forceinline__ int cell_of(float y, float inv32, float off32) {
+// Grid cell of y as the byte offset of its 8-byte record: with u = sat(y * inv32 + off32) in [0, 1], the low mantissa
+// bits of fma(u, 248, 1.5 * 2^23) hold j = rn(248 u) in [0, 248]; j & 0xF8 = 8 * (j >> 3), cell j >> 3 in [0, 31].
+// Any monotone cell function serves: the records are derived from the function itself (build_head_tables).
+__device__ __forceinline__ uint32_t cell_offset(float y, float inv32, float off32) {
     const float u = __saturatef(fmaf(y, inv32, off32));
-    return __float_as_int(fmaf(u, 31.f, 12582912.f)) & 31;
+    return __float_as_uint(fmaf(u, 248.f, 12582912.f)) & 0xF8u;
 }
+__device__ __forceinline__ int cell_of(float y, float inv32, float off32) { return (int)(cell_offset(y, inv32, off32) >> 3); }
 
 // One warp derives the tables of one codebook (lane = grid cell, lanes 1..15 also own a threshold).
 __device__ void build_head_tables(HeadTables& ht, const float* cb_global, int lane) {
@@ -299,6 +304,11 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+__device__ __forceinline__ float2 lds_f2(uint32_t addr) {              // tables that no longer change once built
+    float2 v;
+    asm("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -315,7 +325,7 @@ __device__ __forceinline__ void stage_row(uint32_t buf, const void* x, int64_t i
 // never reads their sign bits or norms skip the projections altogether.
 template <int DT, bool ROTATE, bool SIGNS>
 __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQuantArgs a) {
-    extern __shared__ __align__(16) unsigned char fq_smem[];
+    extern __shared__ __align__(256) unsigned char fq_smem[];
     const int n_tabs = a.cb_per_head ? a.H : 1;
     HeadTables* tabs = reinterpret_cast<HeadTables*>(fq_smem);
     uint4* gfrag_all = reinterpret_cast<uint4*>(fq_smem + sizeof(HeadTables) * n_tabs);
@@ -347,6 +357,7 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
         }
         const HeadTables& ht = tabs[a.cb_per_head ? h : 0];
         const float inv32 = ht.inv32, off32 = ht.off32, guard = ht.guard;
+        const uint32_t cell_base = (uint32_t)__cvta_generic_to_shared(ht.cell2);        // 256-byte aligned
         const int64_t in_base = b * a.xs_b + (int64_t)h * a.xs_h + 32 * t;
         const int64_t out_base = b * a.os_b + (int64_t)h * a.os_h + (a.out_offsets ? a.out_offsets[b] : a.out_offset);
 
@@ -396,11 +407,17 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float2 rec = ht.cell2[cell_of(y[i], inv32, off32)];
-                    const int c = __float_as_int(rec.y) + (y[i] >= rec.x ? 1 : 0);
-                    codes[i >> 3] |= (uint32_t)c << (4 * (i & 7));
-                    y[i] = __fsub_rn(y[i], ht.cb[c]);
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t word = 0u;
+#pragma unroll
+                    for (int k = 7; k >= 0; --k) {                 // last element first: element 8q ends in the low nibble
+                        const int i = 8 * q + k;
+                        const float2 rec = lds_f2(cell_offset(y[i], inv32, off32) | cell_base);
+                        const int c = __float_as_int(rec.y) + (y[i] >= rec.x ? 1 : 0);
+                        word = word * 16u + (uint32_t)c;
+                        y[i] = __fsub_rn(y[i], ht.cb[c]);
+                    }
+                    codes[q] = word;
                 }
             }
             if (!SIGNS) {
