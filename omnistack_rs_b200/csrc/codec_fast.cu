@@ -300,6 +300,7 @@ __device__ __forceinline__ void rotate_row32(float (&y)[32], int t) {
 // and buffer: chunk k of lane l at (k * 32 + l) * 16 bytes (conflict-free 16-byte reads).
 constexpr int kStageChunks = 8;                                     // room for the widest element type
 constexpr int kStageBytesPerWarp = kStageChunks * 32 * 16;          // one buffer: it is refilled as soon as it is read
+constexpr int kBallotBytesPerWarp = 64;                             // the 16 sign ballots of a group, handed from lane 0 to the lanes
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(dst), "l"(src) : "memory");
 }
@@ -307,6 +308,14 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __device__ __forceinline__ float2 lds_f2(uint32_t addr) {              // tables that no longer change once built
     float2 v;
     asm("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_u4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
     return v;
 }
 __device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
@@ -334,6 +343,11 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
     uint4* gfrag = gfrag_all + (size_t)warp * 16 * 32 + lane;      // this lane's 16 A fragments, 32 uint4 apart
     const uint32_t stage = (uint32_t)__cvta_generic_to_shared(gfrag_all + (size_t)kFqWarps * 16 * 32) +
                            warp * kStageBytesPerWarp + lane * 16;  // this lane's chunk 0 of buffer 0
+    // sign ballots of a group: written by lane 0 as [m-tile][column parity][half], read back by lane (g, t) as the
+    // pair (m-tile t, parity g & 1, halves 0 and 1)
+    const uint32_t ballots = (uint32_t)__cvta_generic_to_shared(gfrag_all + (size_t)kFqWarps * 16 * 32) +
+                             kFqWarps * kStageBytesPerWarp + warp * kBallotBytesPerWarp;
+    const uint32_t my_ballots = ballots + (uint32_t)(t * 4 + (g & 1) * 2) * 4;
 
     for (int h = warp; h < n_tabs; h += kFqWarps) build_head_tables(tabs[h], a.codebooks + h * 16, lane);
     __syncthreads();
@@ -482,45 +496,65 @@ __global__ void __launch_bounds__(kFqWarps * 32, 2) fast_quantize_kernel(FastQua
             // ---- sign / ambiguity bits: C element (mt, j) = projection 16mt + g + 8(j>>1) of row 2t + (j&1) ----
             // Ballot words are warp-uniform; lane (row g, quarter t) needs those of m-tile t, column parity g & 1,
             // halves 0 and 1, and keeps them as the m-tiles go by.
-            const bool deg0 = __shfl_sync(kFullMask, (int)degenerate, 8 * t) != 0;         // row 2t   (lanes 8t..)
-            const bool deg1 = __shfl_sync(kFullMask, (int)degenerate, 8 * t + 4) != 0;     // row 2t+1
-            const bool odd = (g & 1) != 0;
-            uint32_t ws0 = 0u, ws1 = 0u, wa0 = 0u, wa1 = 0u;
+            // Sign ballots are warp-uniform; lane (row g, quarter t) needs those of m-tile t, column parity g & 1,
+            // halves 0 and 1: lane 0 leaves all sixteen in shared memory and every lane reads its pair.  A projection
+            // inside the band, or a row that could not be scaled, is rare: one vote tells whether the group has any,
+            // and only then are the sixteen ambiguity ballots taken.
+            bool undecided = degenerate;
 #pragma unroll
             for (int mt = 0; mt < 4; ++mt) {
-                uint32_t bs[4], ba[4];
+                uint32_t sgn[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int sum64 = chi[mt][j] * 256 + clo[mt][j];
-                    bs[j] = __ballot_sync(kFullMask, sum64 >= 64);
-                    ba[j] = __ballot_sync(kFullMask, (uint32_t)sum64 <= 128u || ((j & 1) ? deg1 : deg0));
+                    sgn[j] = __ballot_sync(kFullMask, sum64 >= 64);
+                    undecided = undecided || ((uint32_t)sum64 <= 128u);
                 }
-                const bool mine = (t == mt);
-                ws0 = mine ? (odd ? bs[1] : bs[0]) : ws0; ws1 = mine ? (odd ? bs[3] : bs[2]) : ws1;
-                wa0 = mine ? (odd ? ba[1] : ba[0]) : wa0; wa1 = mine ? (odd ? ba[3] : ba[2]) : wa1;
+                if (lane == 0) sts_u4(ballots + 16 * mt, sgn[0], sgn[2], sgn[1], sgn[3]);
             }
+            __syncwarp();
+            const uint2 wsp = lds_u2(my_ballots);
+            const uint32_t ws0 = wsp.x, ws1 = wsp.y;
+            __syncwarp();                                       // the ballots are read before the next group overwrites them
             const int sh = g >> 1;                              // the C owner of this row's columns has t'' = g >> 1
             uint32_t bits16 = every_fourth_bit(ws0, sh) | (every_fourth_bit(ws1, sh) << 8);
-            uint32_t amb16 = every_fourth_bit(wa0, sh) | (every_fourth_bit(wa1, sh) << 8);
-            if (!active) amb16 = 0u;
-            // ---- exact recomputation of the undecided projections, one per row at a time ------------------
-            uint64_t pending = (uint64_t)__shfl_sync(kFullMask, amb16, 4 * g) |
-                               ((uint64_t)__shfl_sync(kFullMask, amb16, 4 * g + 1) << 16) |
-                               ((uint64_t)__shfl_sync(kFullMask, amb16, 4 * g + 2) << 32) |
-                               ((uint64_t)__shfl_sync(kFullMask, amb16, 4 * g + 3) << 48);
-            while (__any_sync(kFullMask, pending != 0ull)) {
-                const bool have = pending != 0ull;
-                const int pi = have ? __ffsll((long long)pending) - 1 : 0;
-                if (have) pending &= pending - 1ull;
-                const uint32_t gw = __ldg(grow + pi * 4 + t);
-                double acc = 0.0;
+            if (__any_sync(kFullMask, undecided)) {
+                const bool deg0 = __shfl_sync(kFullMask, (int)degenerate, 8 * t) != 0;         // row 2t   (lanes 8t..)
+                const bool deg1 = __shfl_sync(kFullMask, (int)degenerate, 8 * t + 4) != 0;     // row 2t+1
+                const bool odd = (g & 1) != 0;
+                uint32_t wa0 = 0u, wa1 = 0u;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) { const double ev = (double)y[i]; acc += ((gw >> i) & 1u) ? ev : -ev; }
-                acc += __shfl_xor_sync(kFullMask, acc, 1);
-                acc += __shfl_xor_sync(kFullMask, acc, 2);
-                if (have && t == (pi >> 4)) {
-                    const uint32_t m = 1u << (pi & 15);
-                    bits16 = (acc >= 0.0) ? (bits16 | m) : (bits16 & ~m);
+                for (int mt = 0; mt < 4; ++mt) {
+                    uint32_t ba[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int sum64 = chi[mt][j] * 256 + clo[mt][j];
+                        ba[j] = __ballot_sync(kFullMask, (uint32_t)sum64 <= 128u || ((j & 1) ? deg1 : deg0));
+                    }
+                    const bool mine = (t == mt);
+                    wa0 = mine ? (odd ? ba[1] : ba[0]) : wa0; wa1 = mine ? (odd ? ba[3] : ba[2]) : wa1;
+                }
+                uint32_t amb16 = every_fourth_bit(wa0, sh) | (every_fourth_bit(wa1, sh) << 8);
+                if (!active) amb16 = 0u;
+                // ---- exact recomputation of the undecided projections, one per row at a time --------------
+                uint64_t pending = (uint64_t)__shfl_sync(kFullMask, amb16, 4 * g) |
+                                   ((uint64_t)__shfl_sync(kFullMask, amb16, 4 * g + 1) << 16) |
+                                   ((uint64_t)__shfl_sync(kFullMask, amb16, 4 * g + 2) << 32) |
+                                   ((uint64_t)__shfl_sync(kFullMask, amb16, 4 * g + 3) << 48);
+                while (__any_sync(kFullMask, pending != 0ull)) {
+                    const bool have = pending != 0ull;
+                    const int pi = have ? __ffsll((long long)pending) - 1 : 0;
+                    if (have) pending &= pending - 1ull;
+                    const uint32_t gw = __ldg(grow + pi * 4 + t);
+                    double acc = 0.0;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) { const double ev = (double)y[i]; acc += ((gw >> i) & 1u) ? ev : -ev; }
+                    acc += __shfl_xor_sync(kFullMask, acc, 1);
+                    acc += __shfl_xor_sync(kFullMask, acc, 2);
+                    if (have && t == (pi >> 4)) {
+                        const uint32_t m = 1u << (pi & 15);
+                        bits16 = (acc >= 0.0) ? (bits16 | m) : (bits16 & ~m);
+                    }
                 }
             }
             // ---- stores ----------------------------------------------------------------------------------
@@ -600,7 +634,7 @@ static int32_t launch_fast_t(const FastQuantArgs& a, int rotate, cudaStream_t st
     OMNI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int n_tabs = a.cb_per_head ? a.H : 1;
     const size_t smem = sizeof(HeadTables) * n_tabs + (size_t)kFqWarps * 16 * 32 * sizeof(uint4) +
-                        (size_t)kFqWarps * kStageBytesPerWarp;
+                        (size_t)kFqWarps * (kStageBytesPerWarp + kBallotBytesPerWarp);
     const int64_t pairs = a.B * a.H;
     int64_t blocks = (pairs + kFqWarps - 1) / kFqWarps;
     if (blocks > 2 * sms) blocks = 2 * sms;
@@ -616,7 +650,7 @@ static int32_t launch_fast_t(const FastQuantArgs& a, int rotate, cudaStream_t st
         for (const auto& p : done) seen = seen || (p.first == key && p.second == dev);
         if (!seen) {
             const size_t smem_max = sizeof(HeadTables) * kFqMaxHeads + (size_t)kFqWarps * 16 * 32 * sizeof(uint4) +
-                                    (size_t)kFqWarps * kStageBytesPerWarp;
+                                    (size_t)kFqWarps * (kStageBytesPerWarp + kBallotBytesPerWarp);
             OMNI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
             done.emplace_back(key, dev);
         }
