@@ -349,6 +349,8 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
         "cpu_baseline": cpu,
         "e2e": {"value": users * world / e2e_s_step, "unit": "users/s", "h2d_bytes_per_step": host.h2d_bytes,
                 "d2h_bytes_per_step": host.d2h_bytes, "ms_per_step": e2e_s_step * 1e3, "chunks": host.n_chunks, "splits": host.n_splits,
+                "transfer": ("kernels read q from and write rows to the page-locked host buffers (one launch)"
+                             if host.mode == "direct" else "staged copies pipelined over user chunks"),
                 "matches_device_path": e2e_ok},
         "verify": verify,
         "gpu_launches": steps * launches,

@@ -280,12 +280,17 @@ int32_t omni_diag_bounded_wait(int32_t poll_limit, int32_t* status_word, void* s
 
 /* One decode step with HOST query / result buffers (the serving loop of
  * scripts/run_criteo_benchmark.py:481-560, where q arrives per step and the cache is
- * resident): copies q_host -> q_stage (device), runs omni_qattn_decode, copies the
- * result out_stage (device) -> out_host, in `n_chunks` user chunks pipelined over
- * two internal streams, and returns after everything has completed.  q_host/out_host
- * should be page-locked.  Remaining arguments as in omni_qattn_decode; with n_splits > 1 the workspace
- * must hold two slices of omni_qattn_workspace_bytes(ceil(B / n_chunks), Hq, T, n_splits) bytes (one per
- * internal stream).  status_word: device int32 or NULL, as in omni_qattn_decode. */
+ * resident); returns after everything has completed.
+ *   - q_host and out_host page-locked (cudaHostAlloc / cudaHostRegister, e.g. a pinned torch tensor): the attention
+ *     kernels read the queries and write the result rows in host memory themselves, so the transfer overlaps the
+ *     attention work completely; q_stage / out_stage may be NULL, and a call without split-K (or whose workspace
+ *     holds the partial states of all B users) is one launch whatever n_chunks says;
+ *   - otherwise: q_host -> q_stage (device), omni_qattn_decode, out_stage (device) -> out_host, in `n_chunks` user
+ *     chunks pipelined over two internal streams (the environment variable OMNI_HOST_STEP=staged selects this form
+ *     for page-locked buffers as well).
+ * Remaining arguments as in omni_qattn_decode; with n_splits > 1 the workspace must hold two slices of
+ * omni_qattn_workspace_bytes(ceil(B / n_chunks), Hq, T, n_splits) bytes (one per internal stream).
+ * status_word: device int32 or NULL, as in omni_qattn_decode. */
 int32_t omni_qattn_decode_host(const void* q_host, int32_t q_dtype, void* q_stage,
                                const uint8_t* k_nib, const uint8_t* k_qjl, const float* k_norms,
                                const uint8_t* v_nib,

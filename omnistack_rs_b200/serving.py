@@ -9,6 +9,7 @@ block of users and no collective is needed on the data path.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -166,11 +167,13 @@ class QuantizedKVCache:
 
 
 class HostDecodeStep:
-    """One serving step with HOST buffers: query in page-locked host memory -> device,
-    fused attention over the resident cache, result back to page-locked host memory.  The
-    copies and kernels of consecutive user chunks overlap on two internal streams
-    (``omni_qattn_decode_host``).  The cache tensors must be complete before the first call
-    (the internal streams do not wait on the caller's stream)."""
+    """One serving step with HOST buffers (``omni_qattn_decode_host``): the query comes from host memory, the fused
+    attention runs over the resident cache, the result lands in page-locked host memory.  With a page-locked query
+    tensor the kernels read and write the host buffers themselves (``mode == "direct"``: the transfer overlaps the
+    attention work, one launch); a pageable query tensor is staged through device buffers in user chunks whose
+    copies and kernels overlap on two internal streams (``"staged"``; ``OMNI_HOST_STEP=staged`` forces it).  The
+    cache tensors must be complete before the first call (the internal streams do not wait on the caller's
+    stream)."""
 
     def __init__(self, k_nib, k_qjl, k_norms, v_nib, codebooks, n_heads: int, batch: int, q_dtype=torch.bfloat16,
                  user_id=0, seq_lens=None, cache_slots=None, scale: Optional[float] = None, with_qjl: bool = True,
@@ -198,8 +201,8 @@ class HostDecodeStep:
         self.ws_bytes = 2 * self.lib.omni_qattn_workspace_bytes(per_chunk, n_heads, T, self.n_splits)
         self.ws = torch.empty(max(self.ws_bytes // 4, 1), dtype=torch.float32, device=self.dev)
         shape = (batch, n_heads, T, HEAD_DIM)
-        self.q_stage = torch.empty(shape, dtype=q_dtype, device=self.dev)
-        self.out_stage = torch.empty(shape, dtype=torch.float32, device=self.dev)
+        self.q_stage = self.out_stage = None            # device staging: allocated when a step first needs it
+        self.mode = None                                # "direct" / "staged": how the last step moved its data
         self.q_host = torch.empty(shape, dtype=q_dtype).pin_memory()
         self.out_host = torch.empty(shape, dtype=torch.float32).pin_memory()
         self.h2d_bytes = self.q_host.numel() * self.q_host.element_size()
@@ -211,6 +214,11 @@ class HostDecodeStep:
         src = self.q_host if q_host is None else q_host
         if src.is_cuda or src.shape != self.q_host.shape or src.dtype != self.q_dtype or not src.is_contiguous():
             raise ValueError("q_host must be a contiguous CPU tensor of the step's shape and dtype")
+        direct = src.is_pinned() and not os.environ.get("OMNI_HOST_STEP", "").startswith("s")
+        self.mode = "direct" if direct else "staged"
+        if not direct and self.q_stage is None:
+            self.q_stage = torch.empty(self.q_host.shape, dtype=self.q_dtype, device=self.dev)
+            self.out_stage = torch.empty(self.q_host.shape, dtype=torch.float32, device=self.dev)
         with torch.cuda.device(self.dev):
             _lib.check(self.lib.omni_qattn_decode_host(
                 _lib.ptr(src), _lib.DTYPE_CODE[self.q_dtype], _lib.ptr(self.q_stage),

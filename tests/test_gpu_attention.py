@@ -207,6 +207,33 @@ def test_host_buffer_step_matches_device_call(dev):
     assert step.h2d_bytes == 10 * 4 * 128 * 2 and step.d2h_bytes == 10 * 4 * 128 * 4
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,S,n_splits,n_chunks", [(10, 4, 2, 96, None, 3), (6, 8, 2, 700, 3, 1), (9, 8, 2, 400, 2, 4),
+                                                          (300, 2, 2, 130, None, 2)])
+def test_host_buffer_step_direct_and_staged(dev, B, Hq, Hkv, S, n_splits, n_chunks, monkeypatch):
+    """The host-buffer step reads and writes page-locked buffers from the kernels themselves (one launch, or one per
+    chunk when the split-K workspace was sized per chunk); pageable query tensors and OMNI_HOST_STEP=staged take the
+    staged two-stream pipeline.  All forms return the rows of the device-resident call bit for bit."""
+    fa = attn_mod()
+    from omnistack_rs_b200.serving import HostDecodeStep
+    kn, kq, kr, vn, cb, gen = make_cache(B, Hkv, S, seed=B + S, user_id=2)
+    cache = to_dev(dev, kn, kq, kr, vn)
+    lens = torch.randint(1, S + 1, (B,), generator=gen, dtype=torch.int32)
+    q = torch.randn(B, Hq, 1, 128, generator=gen).to(torch.bfloat16)
+    step = HostDecodeStep(*cache, cb, n_heads=Hq, batch=B, q_dtype=torch.bfloat16, user_id=2, seq_lens=lens,
+                          n_chunks=n_chunks, n_splits=n_splits)
+    ref = fa.omni_attn(q.to(dev), *cache, cb.to(dev), user_id=2, seq_lens=lens.to(dev), n_splits=step.n_splits).cpu()
+    step.q_host.copy_(q)
+    monkeypatch.delenv("OMNI_HOST_STEP", raising=False)
+    direct = step.step().clone()
+    assert step.mode == "direct" and step.q_stage is None
+    pageable = step.step(q.clone()).clone()                    # a pageable query tensor: staged
+    assert step.mode == "staged" and step.q_stage is not None
+    monkeypatch.setenv("OMNI_HOST_STEP", "staged")
+    staged = step.step().clone()
+    assert step.mode == "staged"
+    assert torch.equal(direct, ref) and torch.equal(pageable, ref) and torch.equal(staged, ref)
+
+
 def test_serving_shape_slice_against_oracle(dev):
     """Box-scale serving shape (32 kv = 32 q heads, 2048 keys) on a 4-user slice."""
     fa = attn_mod()
