@@ -10,12 +10,15 @@
 //     O[col, d]   += sum_key P[col, key] * V^[key, d]                                            (tcgen05.mma, TS)
 // Q' = [f q | f c (q.g)] and K' = [cb[code] | +-norm] in fp16, so the QJL score correction rides in the same product
 // (c = sqrt(2/pi)/128, f = scale * log2(e) / post with a power-of-two post-scale that keeps fp16 operands below 2^10).
-// S, P (fp16, the A operand of the second product) and O live in tensor memory; thread c of the CTA owns lane c =
-// column c of all three, so the online softmax is thread-local: no shuffles, no cross-lane maxima.
+// S, P (fp16, the A operand of the second product) and O live in tensor memory; lane c of all three is column c, and
+// the two threads (c, half 0) and (c, half 1) share it: each takes 64 of a tile's 128 keys in the softmax (they hand
+// each other their partial maxima through shared memory; the running sum is merged once per work item) and 64 of the
+// 128 output dims when O is rescaled or read out.
 //
-// One CTA of 128 threads per SM.  Per tile: thread k dequantises key k (table lookups as in the warp-level kernel:
-// byte -> half2 of two centroids, table replicated per lane) and writes its K' row (K-major core-matrix layout) and V^
-// row (MN-major) to shared memory; one thread issues the MMAs; completion comes back through mbarriers
+// One CTA of 256 threads per SM (two warps per scheduler: the phases below are latency-bound, not throughput-bound).
+// Per tile: thread (k, 0) dequantises the K' row of key k (table lookups as in the warp-level kernel: byte -> half2 of
+// two centroids, table replicated per lane; K-major core-matrix layout), thread (k, 1) its V^ row (MN-major); one
+// thread issues the MMAs; completion comes back through mbarriers
 // (tcgen05.commit), every wait on them bounded.  The q.g projections of the prologue are a tcgen05 product as well
 // (Q against the +-1 matrix G expanded to fp16).  Operand layouts are the canonical no-swizzle forms: K-major
 // ((8 rows x 16 B) core matrices, LBO between the two K chunks of an instruction, SBO between row groups) and
@@ -31,7 +34,8 @@
 
 namespace omni {
 
-constexpr int kUThreads = 128;                 // threads per CTA = keys per tile = columns per work item (at most)
+constexpr int kUTile = 128;                    // keys per tile = columns per work item (at most) = tensor-memory lanes
+constexpr int kUThreads = 256;                 // threads per CTA: two per column / key, thread (x = tid & 127, half = tid >> 7)
 constexpr int kUKdim = 192;                    // contraction length of the score product: 128 dims + 64 projections
 constexpr uint32_t kULbo = 128;                // K-major operands: bytes between the two 8-element K chunks of an MMA
 constexpr uint32_t kUSbo = (kUKdim / 8) * 128; // ... and between groups of 8 rows (24 core matrices of 128 B)
@@ -41,7 +45,8 @@ constexpr uint32_t kUVSbo = 128;               // MN-major V^: bytes between chu
 constexpr uint32_t kUVLbo = 16 * 128;          // ... and between groups of 8 keys
 constexpr uint32_t kUVBytes = 128 * 128 * 2;
 constexpr uint32_t kUSignTabBytes = 256 * 16;  // byte of 8 sign bits -> four words of fp16 sign masks
-constexpr uint32_t kUSmallBytes = kUSignTabBytes + 256;
+constexpr uint32_t kUXchBytes = 2 * kUTile * 4;  // one float per thread: values the two threads of a column hand each other
+constexpr uint32_t kUSmallBytes = kUSignTabBytes + 256 + kUXchBytes + kUTile * 4;
 constexpr int kULutSpan = 65536;
 constexpr int kUSmemBytes = 227 * 1024;
 constexpr uint32_t kUTmemCols = 512;
@@ -173,6 +178,7 @@ template <int DT>
 __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, int64_t n_items) {
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int x = tid & (kUTile - 1), half = tid >> 7;             // column / key of this thread, and which half of the work
     {   // a codebook the fp16 tables cannot hold to the error budget: the grid stands down (see qattn.cuh)
         const int n_cb = a.cb_per_head ? a.Hkv * 16 : 16;
         bool wide = false;
@@ -199,6 +205,8 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
     const uint32_t sSign = smem_base + off_small;                       // sign-mask table
     const uint32_t bar_s = sSign + kUSignTabBytes, bar_o = bar_s + 8;   // mbarriers
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_small + kUSignTabBytes + 16);
+    float* xch = reinterpret_cast<float*>(smem + off_small + kUSignTabBytes + 256);          // [256] per-thread hand-over
+    float* post_s = xch + kUThreads;                                                          // [128] per-column post-scale
     const uint32_t lut_lane = smem_base + lut_off + 4 * lane;
 
     // sign-mask table: byte b -> words p = 0..3 with bit 15 / 31 set where bit 2p / 2p+1 of b is CLEAR (a clear bit
@@ -223,13 +231,13 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t t_lane = tmem + ((uint32_t)(32 * warp) << 16);       // this warp's 32 lanes: lane tid = column tid
+    const uint32_t t_lane = tmem + ((uint32_t)(32 * (warp & 3)) << 16); // this warp's 32 lanes: lane x = column x
     uint32_t ph_s = 0, ph_o = 0;                                        // parities of the next completions
     bool ok = true;                                                     // false once a bounded wait has expired
 
     const int Gq = a.Hq / a.Hkv;
     const int ncols_all = Gq * a.T;
-    const int n_ctiles = (ncols_all + kUThreads - 1) / kUThreads;
+    const int n_ctiles = (ncols_all + kUTile - 1) / kUTile;
     const float qs = a.scale * kULog2e;
     const int ksteps = a.with_qjl ? kUKdim / 16 : 128 / 16;
     int lut_head = -1;
@@ -237,9 +245,9 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
 
     for (int64_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
         int64_t rest = item;
-        const int col0 = kUThreads * (int)(rest % n_ctiles);
+        const int col0 = kUTile * (int)(rest % n_ctiles);
         rest /= n_ctiles;
-        const int ncols = ncols_all - col0 < kUThreads ? ncols_all - col0 : kUThreads;
+        const int ncols = ncols_all - col0 < kUTile ? ncols_all - col0 : kUTile;
         const int hkv = (int)(rest % a.Hkv);
         rest /= a.Hkv;
         const int split = (int)(rest % a.n_splits);
@@ -254,8 +262,8 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
         const int64_t row0 = slot * a.ks_b + (int64_t)hkv * a.ks_h + s0;
         const int nkeys = s1 > s0 ? (int)(s1 - s0) : 0;
         const int64_t paired_limit = (len & ~(int64_t)7) - s0;      // pair layout: key offsets of this split below this
-        const bool col_on = tid < ncols;
-        const int cg = col0 + (col_on ? tid : 0);
+        const bool col_on = x < ncols;
+        const int cg = col0 + (col_on ? x : 0);
         const int64_t qrow = (b * a.Hq + (int64_t)hkv * Gq + cg / a.T) * a.T + (cg % a.T);
 
         // ---- lookup table of this head's centroids (rebuilt only when the head's codebook changes) -----------------
@@ -274,9 +282,9 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
             __syncthreads();
         }
 
-        // ---- prologue: row tid of Q' (zeros for unused columns) ------------------------------------------------------
+        // ---- prologue: row x of Q' (zeros for unused columns), built by the column's first thread -----------------------
         float post = 1.f;
-        {
+        if (half == 0) {
             float qv[128];
             if (col_on) {
 #pragma unroll
@@ -296,26 +304,28 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
             const float mx = amax * fabsf(qs) / lut_scale;
             if (mx > 1024.f) post = exp2f(ceilf(log2f(mx * (1.f / 1024.f))));
             const float f = qs / post / lut_scale;          // score operands: the table's factor taken back out
-            const uint32_t rowq = sQ + (uint32_t)(tid >> 3) * kUSbo + (uint32_t)(tid & 7) * 16;
+            const uint32_t rowq = sQ + (uint32_t)(x >> 3) * kUSbo + (uint32_t)(x & 7) * 16;
 #pragma unroll
             for (int kc = 0; kc < 16; ++kc)
                 u_sts16(rowq + kc * kULbo, u_half2(qv[8 * kc] * f, qv[8 * kc + 1] * f), u_half2(qv[8 * kc + 2] * f, qv[8 * kc + 3] * f),
                         u_half2(qv[8 * kc + 4] * f, qv[8 * kc + 5] * f), u_half2(qv[8 * kc + 6] * f, qv[8 * kc + 7] * f));
+            post_s[x] = post;
         }
+        __syncthreads();                                  // Q' rows and post-scales are complete
+        post = post_s[x];
         if (a.with_qjl) {
             // G of this (user, kv head) as +-1 fp16, K-major [64 projections x 128 dims] in the K' buffer; then
             // (f q).G^T on the tensor cores into S columns 0..63, scaled by c into the last 64 K columns of Q'
             const int32_t uid = a.user_ids ? a.user_ids[b] : a.user_id;
             const uint32_t* grow = a.g_rows + (size_t)seed_of(uid, hkv) * kQjlDim * 4;
-            const int pi = tid >> 1, half = tid & 1;
+            const int pi = tid >> 2, quarter = tid & 3;       // projection row, and which 32 of its 128 signs
             const uint32_t rowg = sK + (uint32_t)(pi >> 3) * kUSbo + (uint32_t)(pi & 7) * 16;
-#pragma unroll
-            for (int wq = 0; wq < 2; ++wq) {
-                const uint32_t gw = __ldg(grow + pi * 4 + 2 * half + wq);
+            {
+                const uint32_t gw = __ldg(grow + pi * 4 + quarter);
 #pragma unroll
                 for (int by = 0; by < 4; ++by) {
                     const uint4 m = u_lds16(sSign + 16 * ((gw >> (8 * by)) & 0xFFu));
-                    u_sts16(rowg + (uint32_t)(8 * half + 4 * wq + by) * kULbo, 0x3C003C00u ^ m.x, 0x3C003C00u ^ m.y, 0x3C003C00u ^ m.z, 0x3C003C00u ^ m.w);
+                    u_sts16(rowg + (uint32_t)(4 * quarter + by) * kULbo, 0x3C003C00u ^ m.x, 0x3C003C00u ^ m.y, 0x3C003C00u ^ m.z, 0x3C003C00u ^ m.w);
                 }
             }
             u_fence_async_smem();
@@ -332,10 +342,10 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
             ph_s ^= 1u;
             if (!ok) break;
             tc_fence_after();
-            const uint32_t rowq = sQ + (uint32_t)(tid >> 3) * kUSbo + (uint32_t)(tid & 7) * 16;
+            const uint32_t rowq = sQ + (uint32_t)(x >> 3) * kUSbo + (uint32_t)(x & 7) * 16;
             const float qjl_mul = kQjlCoef * lut_scale;     // the sign term does not pass through the centroid table
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            {
+                const int j = half;                         // each thread of the column takes 32 of its 64 projections
                 uint32_t v[32];
                 tc_ld32(t_lane + kUColS + 32 * j, v);
                 tc_wait_ld();
@@ -355,61 +365,63 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
         // ---- key tiles ---------------------------------------------------------------------------------------------
         float m_run = -INFINITY, l_run = 0.f;
         bool o_valid = false;                        // O holds a product already (false: the next one overwrites it)
-        // the packed bytes of key tid of a tile, fetched one tile ahead (keys past the end repeat the last one)
-        uint4 kw[4], vw[4];
+        // the packed bytes of key x of a tile, fetched one tile ahead (keys past the end repeat the last one): the K
+        // nibbles, sign bytes and norm by the key's first thread, the V nibbles by its second
+        uint4 nw[4];
         uint2 sb = make_uint2(0u, 0u);
         float nrm = 0.f;
         auto fetch_tile = [&](int k0) {
-            const int nv = nkeys - k0 < kUThreads ? nkeys - k0 : kUThreads;
-            const int64_t ridx = row0 + k0 + (tid < nv ? tid : nv - 1);
-            const uint4* kp = reinterpret_cast<const uint4*>(a.k_nib + ridx * kNibBytes);
-            const uint4* vp = reinterpret_cast<const uint4*>(a.v_nib + ridx * kNibBytes);
+            const int nv = nkeys - k0 < kUTile ? nkeys - k0 : kUTile;
+            const int64_t ridx = row0 + k0 + (x < nv ? x : nv - 1);
+            const uint4* np = reinterpret_cast<const uint4*>((half == 0 ? a.k_nib : a.v_nib) + ridx * kNibBytes);
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) { kw[c4] = u_ldg16(kp + c4); vw[c4] = u_ldg16(vp + c4); }
-            if (a.with_qjl) {
+            for (int c4 = 0; c4 < 4; ++c4) nw[c4] = u_ldg16(np + c4);
+            if (half == 0 && a.with_qjl) {
                 sb = __ldg(reinterpret_cast<const uint2*>(a.k_qjl + ridx * kQjlBytes));
                 nrm = fminf(__ldg(a.k_norms + ridx), 65504.f);
             }
         };
         if (nkeys > 0) fetch_tile(0);
-        for (int k0 = 0; k0 < nkeys; k0 += kUThreads) {
-            const int nvalid = nkeys - k0 < kUThreads ? nkeys - k0 : kUThreads;
-            const uint32_t rowk = sK + (uint32_t)(tid >> 3) * kUSbo + (uint32_t)(tid & 7) * 16;
+        for (int k0 = 0; k0 < nkeys; k0 += kUTile) {
+            const int nvalid = nkeys - k0 < kUTile ? nkeys - k0 : kUTile;
+            bool mine_ok = true;                         // this thread's own bounded wait (made uniform at the next barrier)
+            if (half == 0) {
+                const uint32_t rowk = sK + (uint32_t)(x >> 3) * kUSbo + (uint32_t)(x & 7) * 16;
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-                u_dequant_store(rowk + (uint32_t)(4 * c4 + 0) * kULbo, lut_lane, kw[c4].x);
-                u_dequant_store(rowk + (uint32_t)(4 * c4 + 1) * kULbo, lut_lane, kw[c4].y);
-                u_dequant_store(rowk + (uint32_t)(4 * c4 + 2) * kULbo, lut_lane, kw[c4].z);
-                u_dequant_store(rowk + (uint32_t)(4 * c4 + 3) * kULbo, lut_lane, kw[c4].w);
-            }
-            if (a.with_qjl) {
-                const uint32_t n2 = u_half2(nrm, nrm);
-                const uint32_t sw[2] = {sb.x, sb.y};
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint4 m = u_lds16(sSign + 16 * ((sw[j >> 2] >> (8 * (j & 3))) & 0xFFu));
-                    u_sts16(rowk + (uint32_t)(16 + j) * kULbo, n2 ^ m.x, n2 ^ m.y, n2 ^ m.z, n2 ^ m.w);
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    u_dequant_store(rowk + (uint32_t)(4 * c4 + 0) * kULbo, lut_lane, nw[c4].x);
+                    u_dequant_store(rowk + (uint32_t)(4 * c4 + 1) * kULbo, lut_lane, nw[c4].y);
+                    u_dequant_store(rowk + (uint32_t)(4 * c4 + 2) * kULbo, lut_lane, nw[c4].z);
+                    u_dequant_store(rowk + (uint32_t)(4 * c4 + 3) * kULbo, lut_lane, nw[c4].w);
                 }
-            }
-            // V^ may be overwritten once the previous tile's second product has read it
+                if (a.with_qjl) {
+                    const uint32_t n2 = u_half2(nrm, nrm);
+                    const uint32_t sw[2] = {sb.x, sb.y};
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 m = u_lds16(sSign + 16 * ((sw[j >> 2] >> (8 * (j & 3))) & 0xFFu));
+                        u_sts16(rowk + (uint32_t)(16 + j) * kULbo, n2 ^ m.x, n2 ^ m.y, n2 ^ m.z, n2 ^ m.w);
+                    }
+                }
+            } else {
+            // V^ may be overwritten once the previous tile's second product has read it: only the threads that write it
+            // wait here (the K' rows are dequantised meanwhile); every thread tracks the parity
             if (o_valid) {
-                ok = __syncthreads_and(u_mbar_wait_bounded(bar_o, ph_o)) != 0;
-                ph_o ^= 1u;
-                if (!ok) break;
+                mine_ok = u_mbar_wait_bounded(bar_o, ph_o);
                 tc_fence_after();
             }
-            const uint32_t rowv = sV + (uint32_t)(tid & 7) * 16 + (uint32_t)(tid >> 3) * kUVLbo;
+            const uint32_t rowv = sV + (uint32_t)(x & 7) * 16 + (uint32_t)(x >> 3) * kUVLbo;
             // Pair layout of V (groups of eight keys that lie completely below the user's length): the row of a pair's
             // first key holds the even-d nibbles of both keys, the row of the second key the odd-d ones, so a table
             // lookup yields (first key, second key) at one dim.  The two threads of a pair (lanes l and l ^ 3) exchange
             // their lookups and each keeps its own key's halves: (own low, other low) for the first key, (other high,
             // own high) for the second.  A group is paired as a whole, and groups coincide with runs of eight lanes.
-            const bool v_pair = a.v_paired && (int64_t)(k0 + tid) < paired_limit;
+            const bool v_pair = a.v_paired && (int64_t)(k0 + x) < paired_limit;
             if (__ballot_sync(0xffffffffu, v_pair) != 0u) {
-                const uint32_t sel = v_pair ? ((tid & 2) ? 0x3276u : 0x5410u) : 0x3210u;
+                const uint32_t sel = v_pair ? ((x & 2) ? 0x3276u : 0x5410u) : 0x3210u;
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
-                    const uint32_t ws[4] = {vw[c4].x, vw[c4].y, vw[c4].z, vw[c4].w};
+                    const uint32_t ws[4] = {nw[c4].x, nw[c4].y, nw[c4].z, nw[c4].w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const uint32_t l0 = u_lut<0>(lut_lane, ws[e]), l1 = u_lut<1>(lut_lane, ws[e]);
@@ -423,16 +435,19 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
             } else {
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
-                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 0) * kUVSbo, lut_lane, vw[c4].x);
-                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 1) * kUVSbo, lut_lane, vw[c4].y);
-                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 2) * kUVSbo, lut_lane, vw[c4].z);
-                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 3) * kUVSbo, lut_lane, vw[c4].w);
+                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 0) * kUVSbo, lut_lane, nw[c4].x);
+                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 1) * kUVSbo, lut_lane, nw[c4].y);
+                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 2) * kUVSbo, lut_lane, nw[c4].z);
+                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 3) * kUVSbo, lut_lane, nw[c4].w);
                 }
             }
-            if (k0 + kUThreads < nkeys) fetch_tile(k0 + kUThreads);      // in flight during the products and the softmax
+            }
+            if (o_valid) ph_o ^= 1u;
+            if (k0 + kUTile < nkeys) fetch_tile(k0 + kUTile);            // in flight during the products and the softmax
             u_fence_async_smem();
             tc_fence_before();
-            __syncthreads();
+            ok = __syncthreads_and(mine_ok) != 0;
+            if (!ok) break;
             if (tid == 0) {
                 tc_fence_after();
                 for (int ks = 0; ks < ksteps; ++ks)
@@ -445,14 +460,16 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
             if (!ok) break;
             tc_fence_after();
 
-            // ---- online softmax of column tid over the tile's keys: first the tile maximum, then the weights ------
+            // ---- online softmax of column x over the tile's keys, 64 per thread: first the tile maximum (the two
+            //      threads of a column hand each other theirs), then the weights ------------------------------------
             float tmax = -INFINITY;
 #pragma unroll 1
-            for (int j = 0; j < 4; ++j) {
+            for (int jj = 0; jj < 2; ++jj) {
+                const int j = 2 * half + jj;
                 uint32_t v[32];
                 tc_ld32(t_lane + kUColS + 32 * j, v);
                 tc_wait_ld();
-                if (nvalid == kUThreads) {                     // full tile: no per-key bound checks
+                if (nvalid == kUTile) {                        // full tile: no per-key bound checks
                     float t0 = tmax, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
@@ -466,7 +483,9 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
                         if (32 * j + i < nvalid) tmax = fmaxf(tmax, __uint_as_float(v[i]));
                 }
             }
-            tmax *= post;
+            xch[tid] = tmax;
+            __syncthreads();
+            tmax = fmaxf(tmax, xch[tid ^ kUTile]) * post;
             const bool raise = col_on && tmax > m_run + kUSlack;
             if (__syncthreads_or(raise)) {
                 // lazy reference maximum: raised only when a score exceeds it by 2^kUSlack; the accumulated row of O
@@ -477,7 +496,8 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
                 m_run = m_new;
                 if (o_valid) {
 #pragma unroll 1
-                    for (int j = 0; j < 4; ++j) {
+                    for (int jj = 0; jj < 2; ++jj) {
+                        const int j = 2 * half + jj;           // this thread's 64 of the 128 output dims
                         uint32_t v[32];
                         tc_ld32(t_lane + kUColO + 32 * j, v);
                         tc_wait_ld();
@@ -489,12 +509,13 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
                 }
             }
 #pragma unroll 1
-            for (int j = 0; j < 4; ++j) {
+            for (int jj = 0; jj < 2; ++jj) {
+                const int j = 2 * half + jj;
                 uint32_t v[32];
                 tc_ld32(t_lane + kUColS + 32 * j, v);
                 tc_wait_ld();
                 uint32_t pk[16];
-                if (nvalid == kUThreads) {                     // full tile; unused columns carry the maximum +inf: weights 0
+                if (nvalid == kUTile) {                        // full tile; unused columns carry the maximum +inf: weights 0
                     const float mneg = col_on ? -m_run : -INFINITY;
                     float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
@@ -547,19 +568,24 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
             tc_fence_after();
         }
 
-        // ---- epilogue: row tid of O -> the output row of column tid (or its split-K partial state) ------------------
+        // ---- epilogue: row x of O -> the output row of column x (or its split-K partial state); the column's two
+        //      threads add up their sums of weights and write 64 dims each -------------------------------------------
+        xch[tid] = l_run;
+        __syncthreads();
+        const float l_tot = l_run + xch[tid ^ kUTile];
         float* dst = nullptr;
         float mul = 0.f;
         if (a.n_splits == 1) {
             dst = a.out + qrow * kHeadDim;
-            mul = l_run > 0.f ? 1.f / (l_run * lut_scale) : 0.f;
+            mul = l_tot > 0.f ? 1.f / (l_tot * lut_scale) : 0.f;
         } else {
             float* w = a.ws + (qrow * a.n_splits + split) * kWsStride;
             dst = w;
             mul = 1.f / lut_scale;
-            if (col_on) { w[128] = m_run * 0.6931471805599453f; w[129] = l_run; }
+            if (col_on && half == 0) { w[128] = m_run * 0.6931471805599453f; w[129] = l_tot; }
         }
         if (a.unrotate_out && a.n_splits == 1) {
+          if (half == 0) {                              // the inverse rotation needs the whole row in one thread
             float o[128];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -574,9 +600,11 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
                 for (int i = 0; i < 32; ++i)
                     *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
             }
+          }
         } else {
 #pragma unroll 1
-            for (int j = 0; j < 4; ++j) {
+            for (int jj = 0; jj < 2; ++jj) {
+                const int j = 2 * half + jj;
                 uint32_t v[32];
                 if (o_valid) { tc_ld32(t_lane + kUColO + 32 * j, v); tc_wait_ld(); }
                 if (col_on) {
@@ -614,7 +642,7 @@ static int32_t launch_umma_t(const AttnArgs& a, cudaStream_t st) {
     int dev = 0, sms = 148;
     OMNI_CUDA(cudaGetDevice(&dev));
     OMNI_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    const int64_t n_ctiles = ((int64_t)(a.Hq / a.Hkv) * a.T + kUThreads - 1) / kUThreads;
+    const int64_t n_ctiles = ((int64_t)(a.Hq / a.Hkv) * a.T + kUTile - 1) / kUTile;
     const int64_t items = a.B * a.n_splits * a.Hkv * n_ctiles;
     auto kern = qattn_umma_kernel<DT>;
     {
