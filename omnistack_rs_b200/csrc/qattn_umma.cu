@@ -483,11 +483,14 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
                         if (32 * j + i < nvalid) tmax = fmaxf(tmax, __uint_as_float(v[i]));
                 }
             }
-            xch[tid] = tmax;
-            __syncthreads();
-            tmax = fmaxf(tmax, xch[tid ^ kUTile]) * post;
-            const bool raise = col_on && tmax > m_run + kUSlack;
-            if (__syncthreads_or(raise)) {
+            // The column's maximum over the tile is the larger of its two threads' maxima; it exceeds the threshold
+            // exactly when one of them does, so the hand-over (and its barrier) is needed only when some thread's does.
+            tmax *= post;
+            if (__syncthreads_or(col_on && tmax > m_run + kUSlack)) {
+                xch[tid] = tmax;
+                __syncthreads();
+                tmax = fmaxf(tmax, xch[tid ^ kUTile]);
+                const bool raise = col_on && tmax > m_run + kUSlack;
                 // lazy reference maximum: raised only when a score exceeds it by 2^kUSlack; the accumulated row of O
                 // and the running sum are rescaled (lanes that keep their maximum multiply by one)
                 const float m_new = raise ? fmaxf(m_run, tmax) : m_run;
