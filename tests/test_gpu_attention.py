@@ -409,6 +409,35 @@ def test_longest_first_order_of_ragged_users(dev, per_head, monkeypatch):
         assert (outs["1"][b:b + 1].cpu() - want).abs().max() <= ATOL
 
 
+def test_lora_fold_with_rotation_slots_and_several_column_tiles(dev, monkeypatch):
+    """The folded query update together with the features it sits next to in the prologue: the rotation folded into
+    the query (the update comes first, as the reference applies it to the raw query), cache slots, per-user ids, and
+    twelve query columns per kv head (two tiles, several tokens: one down projection per token)."""
+    fa = attn_mod()
+    from omnistack_rs_b200 import _lib
+    B, Hq, Hkv, T, S, hid, rank = 4, 8, 2, 3, 300, 128, 16
+    kn, kq, kr, vn, cb, gen = make_cache(B + 2, Hkv, S, seed=77, user_id=0)
+    q = torch.randn(B, Hq, T, 128, generator=gen).to(torch.bfloat16)
+    x = torch.randn(B, T, hid, generator=gen)
+    la = torch.randn(3, rank, hid, generator=gen) * 0.05
+    lb = torch.randn(3, Hq * 128, rank, generator=gen) * 0.1
+    idx = torch.tensor([2, -1, 0, 1], dtype=torch.int32)
+    slots = torch.tensor([5, 0, 3, 1], dtype=torch.int32)
+    cache = to_dev(dev, kn, kq, kr, vn, cb)
+    lora = dict(x=x.to(dev), lora_a=la.to(dev), lora_b=lb.to(dev), lora_indices=idx.to(dev), lora_alpha=0.5)
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("OMNI_LORA_FOLD", flag)
+        outs[flag] = fa.omni_attn(q.to(dev), *cache, user_id=0, cache_slots=slots.to(dev), rotate_q=True, n_splits=2, **lora)
+    _lib.check_device_status(dev)
+    assert torch.equal(outs["1"], outs["0"])
+    q_eff = orc.wht128(orc.apply_lora_to_q(q, x, la, lb, idx, 0.5).float())
+    for b in range(B):
+        sl = int(slots[b])
+        want = orc.decode_attention(q_eff[b:b + 1], kn[sl:sl + 1], kq[sl:sl + 1], kr[sl:sl + 1], vn[sl:sl + 1], cb, 0)
+        assert (outs["1"][b:b + 1].cpu() - want).abs().max() <= ATOL, b
+
+
 @pytest.mark.parametrize("n_splits", [16, 37, 200, None])
 def test_single_user_long_cache_many_splits(dev, n_splits):
     """One user, 32 q / 8 kv heads, 6,000 keys: far more key splits than resident warps need, odd split counts,
