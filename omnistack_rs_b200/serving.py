@@ -228,3 +228,53 @@ class HostDecodeStep:
                 self.v_paired, _lib.ptr(self.out_stage), _lib.ptr(self.out_host), self.n_chunks,
                 self.n_splits, _lib.ptr(self.ws), self.ws_bytes, _lib.ptr(_lib.status_word(self.dev))))
         return self.out_host
+
+
+class GraphedAttention:
+    """``omni_attn`` on fixed device buffers, captured once into a CUDA graph and replayed per query.
+
+    Small decode calls (the reference benchmark's 64-user query is 20 us of device work behind about as much host
+    work: Python, two or three kernel launches) are bound by the host when issued one by one; a replayed graph costs
+    one launch.  The query (and, with adapters, the hidden state and adapter indices) lives in buffers owned by this
+    object: write into ``q`` / ``x`` / ``lora_indices`` (or pass tensors to ``__call__``, which copies them in) and
+    read the result from ``out``, which the next replay overwrites.  Everything else -- cache tensors, codebooks,
+    per-user lengths, adapter stacks -- is captured by address, so in-place changes of their contents are seen and the
+    tensors must stay alive (this object keeps references)."""
+
+    def __init__(self, q_shape, q_dtype, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id=0, *, hidden=None,
+                 lora_a=None, lora_b=None, lora_alpha: float = 1.0, **attn_kwargs):
+        from .kernels.fused_attention import omni_attn
+        dev = _lib.require_cuda(k_nibbles, k_qjl, k_norms, v_nibbles)
+        B, _, T, _ = q_shape
+        self.q = torch.zeros(q_shape, dtype=q_dtype, device=dev)
+        self.x = self.lora_indices = None
+        lora = {}
+        if lora_a is not None:
+            self.x = torch.zeros(B, T, lora_a.shape[2] if hidden is None else hidden, dtype=torch.float32, device=dev)
+            self.lora_indices = torch.full((B,), -1, dtype=torch.int32, device=dev)
+            lora = dict(x=self.x, lora_a=lora_a, lora_b=lora_b, lora_indices=self.lora_indices, lora_alpha=lora_alpha)
+        self._keep = (k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, lora_a, lora_b, attn_kwargs)
+
+        def call():
+            return omni_attn(self.q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id=user_id, **lora, **attn_kwargs)
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):                      # first-call set-up (kernel attributes, tensor maps, workspace) is not captured
+                call()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = call()
+
+    def __call__(self, q=None, x=None, lora_indices=None) -> torch.Tensor:
+        if q is not None:
+            self.q.copy_(q, non_blocking=True)
+        if x is not None:
+            self.x.copy_(x, non_blocking=True)
+        if lora_indices is not None:
+            self.lora_indices.copy_(lora_indices, non_blocking=True)
+        self.graph.replay()
+        return self.out

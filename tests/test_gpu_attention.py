@@ -438,6 +438,38 @@ def test_lora_fold_with_rotation_slots_and_several_column_tiles(dev, monkeypatch
         assert (outs["1"][b:b + 1].cpu() - want).abs().max() <= ATOL, b
 
 
+def test_graphed_attention_replays_the_eager_call(dev):
+    """A decode call captured into a CUDA graph (fixed query / adapter-input buffers, everything else by address)
+    gives the eager call's rows on every replay, follows new queries and in-place changes of the cache, and reports
+    an out-of-range adapter index through the status word like the eager call."""
+    fa = attn_mod()
+    from omnistack_rs_b200 import _lib
+    from omnistack_rs_b200.serving import GraphedAttention
+    B, Hq, Hkv, S = 16, 8, 2, 150
+    kn, kq, kr, vn, cb, gen = make_cache(B, Hkv, S, seed=91, user_id=3)
+    cache = list(to_dev(dev, kn, kq, kr, vn, cb))
+    la = (torch.randn(3, 16, 128, generator=gen) * 0.05).to(dev)
+    lb = (torch.randn(3, Hq * 128, 16, generator=gen) * 0.1).to(dev)
+    lens = torch.randint(1, S + 1, (B,), generator=gen, dtype=torch.int32).to(dev)
+    g = GraphedAttention((B, Hq, 1, 128), torch.bfloat16, *cache, user_id=3, lora_a=la, lora_b=lb, lora_alpha=0.4,
+                         seq_lens=lens, n_splits=2)
+    for _ in range(3):
+        q = torch.randn(B, Hq, 1, 128, generator=gen).to(torch.bfloat16).to(dev)
+        x = torch.randn(B, 1, 128, generator=gen).to(dev)
+        idx = torch.randint(-1, 3, (B,), generator=gen, dtype=torch.int32).to(dev)
+        got = g(q, x, idx).clone()
+        want = fa.omni_attn(q, *cache, user_id=3, x=x, lora_a=la, lora_b=lb, lora_indices=idx, lora_alpha=0.4,
+                            seq_lens=lens, n_splits=2)
+        assert torch.equal(got, want)
+    cache[3].copy_(torch.roll(cache[3], 1, dims=2))                  # V rows shifted by one key, in place
+    lens.fill_(S)
+    got = g().clone()
+    want = fa.omni_attn(q, *cache, user_id=3, x=x, lora_a=la, lora_b=lb, lora_indices=idx, lora_alpha=0.4, seq_lens=lens,
+                        n_splits=2)
+    assert torch.equal(got, want)
+    _lib.check_device_status(dev)
+
+
 @pytest.mark.parametrize("n_splits", [16, 37, 200, None])
 def test_single_user_long_cache_many_splits(dev, n_splits):
     """One user, 32 q / 8 kv heads, 6,000 keys: far more key splits than resident warps need, odd split counts,
