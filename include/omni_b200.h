@@ -206,9 +206,14 @@ int32_t omni_lora_q(const void* q, int32_t q_dtype, const float* x, const float*
 
 /* Attention with the per-user low-rank query update in the same call (the reference passes x, lora_a, lora_b,
  * lora_indices and lora_alpha to `omni_attn`, kernels/fused_attention.py:537-560, and applies them in the
- * kernel prologue :166-191).  `lora` == NULL makes this omni_qattn_decode.  Otherwise the update runs first on
- * the same stream into the front of `workspace`, which must hold omni_qattn_lora_workspace_bytes(...) bytes
- * (the updated fp32 queries, then the split-K partial states); q may be of any q_dtype.                      */
+ * kernel prologue :166-191).  `lora` == NULL makes this omni_qattn_decode.  Otherwise the update is applied in the
+ * prologue of the attention kernel that serves the call (the warp that owns a tile of query columns computes the
+ * down projection and its columns' part of the up projection) when that is the warp-level tensor-core kernel and
+ * the adapter is small (rank <= 32, rank * hidden <= 8192); for other calls it runs first on the same stream as a
+ * launch of its own, into the front of `workspace`.  Both forms give the same bits.  The environment variable
+ * OMNI_LORA_FOLD=0 / 1 forces the separate launch / the fold.  `workspace` must hold
+ * omni_qattn_lora_workspace_bytes(...) bytes either way (room for the updated fp32 queries, then the split-K
+ * partial states); q may be of any q_dtype.                                                                  */
 typedef struct omni_lora {
     const float*   x;             /* device fp32 [B][T][hidden]                 */
     const float*   lora_a;        /* device fp32 [n_adapters][rank][hidden]     */
