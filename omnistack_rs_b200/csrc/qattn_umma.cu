@@ -147,6 +147,11 @@ __device__ __forceinline__ uint32_t u_lut(uint32_t lut_lane, uint32_t w) {
 __device__ __forceinline__ void u_sts16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+__device__ __forceinline__ uint4 u_lds16_const(uint32_t addr) {        // tables that do not change while they are read
+    uint4 v;
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ uint4 u_lds16(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -155,6 +160,24 @@ __device__ __forceinline__ uint4 u_lds16(uint32_t addr) {
 // eight centroids of one packed word as a 16-byte chunk of fp16
 __device__ __forceinline__ void u_dequant_store(uint32_t dst, uint32_t lut_lane, uint32_t w) {
     u_sts16(dst, u_lut<0>(lut_lane, w), u_lut<1>(lut_lane, w), u_lut<2>(lut_lane, w), u_lut<3>(lut_lane, w));
+}
+// A whole 64-byte row (16 packed words -> 16 chunks `stride` bytes apart) in two batches of 32 table lookups followed by
+// their 8 stores: a store cannot be moved above a load of the same memory space, so lookups written chunk by chunk
+// would each wait out the table's latency before the next chunk's could be issued.
+__device__ __forceinline__ void u_dequant_row(uint32_t dst, uint32_t stride, uint32_t lut_lane, const uint4 (&nw)[4]) {
+#pragma unroll
+    for (int hb = 0; hb < 2; ++hb) {
+        const uint32_t w[8] = {nw[2 * hb].x, nw[2 * hb].y, nw[2 * hb].z, nw[2 * hb].w,
+                               nw[2 * hb + 1].x, nw[2 * hb + 1].y, nw[2 * hb + 1].z, nw[2 * hb + 1].w};
+        uint32_t l[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            l[i][0] = u_lut<0>(lut_lane, w[i]); l[i][1] = u_lut<1>(lut_lane, w[i]);
+            l[i][2] = u_lut<2>(lut_lane, w[i]); l[i][3] = u_lut<3>(lut_lane, w[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) u_sts16(dst + (uint32_t)(8 * hb + i) * stride, l[i][0], l[i][1], l[i][2], l[i][3]);
+    }
 }
 // in-thread normalised 128-point Walsh-Hadamard transform (stage order h = 1 .. 64, one rounding per operation)
 __device__ __forceinline__ void u_wht128(float (&v)[128]) {
@@ -387,21 +410,16 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
             bool mine_ok = true;                         // this thread's own bounded wait (made uniform at the next barrier)
             if (half == 0) {
                 const uint32_t rowk = sK + (uint32_t)(x >> 3) * kUSbo + (uint32_t)(x & 7) * 16;
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    u_dequant_store(rowk + (uint32_t)(4 * c4 + 0) * kULbo, lut_lane, nw[c4].x);
-                    u_dequant_store(rowk + (uint32_t)(4 * c4 + 1) * kULbo, lut_lane, nw[c4].y);
-                    u_dequant_store(rowk + (uint32_t)(4 * c4 + 2) * kULbo, lut_lane, nw[c4].z);
-                    u_dequant_store(rowk + (uint32_t)(4 * c4 + 3) * kULbo, lut_lane, nw[c4].w);
-                }
+                u_dequant_row(rowk, kULbo, lut_lane, nw);
                 if (a.with_qjl) {
                     const uint32_t n2 = u_half2(nrm, nrm);
                     const uint32_t sw[2] = {sb.x, sb.y};
+                    uint4 m[8];                              // all eight mask lookups before the first store (see u_dequant_row)
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint4 m = u_lds16(sSign + 16 * ((sw[j >> 2] >> (8 * (j & 3))) & 0xFFu));
-                        u_sts16(rowk + (uint32_t)(16 + j) * kULbo, n2 ^ m.x, n2 ^ m.y, n2 ^ m.z, n2 ^ m.w);
-                    }
+                    for (int j = 0; j < 8; ++j) m[j] = u_lds16_const(sSign + 16 * ((sw[j >> 2] >> (8 * (j & 3))) & 0xFFu));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        u_sts16(rowk + (uint32_t)(16 + j) * kULbo, n2 ^ m[j].x, n2 ^ m[j].y, n2 ^ m[j].z, n2 ^ m[j].w);
                 }
             } else {
             // V^ may be overwritten once the previous tile's second product has read it: only the threads that write it
@@ -420,26 +438,25 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
             if (__ballot_sync(0xffffffffu, v_pair) != 0u) {
                 const uint32_t sel = v_pair ? ((x & 2) ? 0x3276u : 0x5410u) : 0x3210u;
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    const uint32_t ws[4] = {nw[c4].x, nw[c4].y, nw[c4].z, nw[c4].w};
+                for (int hb = 0; hb < 2; ++hb) {
+                    const uint32_t ws[8] = {nw[2 * hb].x, nw[2 * hb].y, nw[2 * hb].z, nw[2 * hb].w,
+                                            nw[2 * hb + 1].x, nw[2 * hb + 1].y, nw[2 * hb + 1].z, nw[2 * hb + 1].w};
+                    uint32_t l[8][4];                        // 32 lookups, then their exchanges and eight stores
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const uint32_t l0 = u_lut<0>(lut_lane, ws[e]), l1 = u_lut<1>(lut_lane, ws[e]);
-                        const uint32_t l2 = u_lut<2>(lut_lane, ws[e]), l3 = u_lut<3>(lut_lane, ws[e]);
-                        const uint32_t o0 = __shfl_xor_sync(0xffffffffu, l0, 3), o1 = __shfl_xor_sync(0xffffffffu, l1, 3);
-                        const uint32_t o2 = __shfl_xor_sync(0xffffffffu, l2, 3), o3 = __shfl_xor_sync(0xffffffffu, l3, 3);
-                        u_sts16(rowv + (uint32_t)(4 * c4 + e) * kUVSbo, __byte_perm(l0, o0, sel), __byte_perm(l1, o1, sel),
-                                __byte_perm(l2, o2, sel), __byte_perm(l3, o3, sel));
+                    for (int e = 0; e < 8; ++e) {
+                        l[e][0] = u_lut<0>(lut_lane, ws[e]); l[e][1] = u_lut<1>(lut_lane, ws[e]);
+                        l[e][2] = u_lut<2>(lut_lane, ws[e]); l[e][3] = u_lut<3>(lut_lane, ws[e]);
                     }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) l[e][k] = __byte_perm(l[e][k], __shfl_xor_sync(0xffffffffu, l[e][k], 3), sel);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) u_sts16(rowv + (uint32_t)(8 * hb + e) * kUVSbo, l[e][0], l[e][1], l[e][2], l[e][3]);
                 }
             } else {
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 0) * kUVSbo, lut_lane, nw[c4].x);
-                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 1) * kUVSbo, lut_lane, nw[c4].y);
-                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 2) * kUVSbo, lut_lane, nw[c4].z);
-                    u_dequant_store(rowv + (uint32_t)(4 * c4 + 3) * kUVSbo, lut_lane, nw[c4].w);
-                }
+                u_dequant_row(rowv, kUVSbo, lut_lane, nw);
             }
             }
             if (o_valid) ph_o ^= 1u;
@@ -463,12 +480,14 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
             // ---- online softmax of column x over the tile's keys, 64 per thread: first the tile maximum (the two
             //      threads of a column hand each other theirs), then the weights ------------------------------------
             float tmax = -INFINITY;
-#pragma unroll 1
+            uint32_t sv[2][32];                                // this thread's 64 scores: both loads in flight, one wait
+            tc_ld32(t_lane + kUColS + 64 * half, sv[0]);
+            tc_ld32(t_lane + kUColS + 64 * half + 32, sv[1]);
+            tc_wait_ld();
+#pragma unroll
             for (int jj = 0; jj < 2; ++jj) {
                 const int j = 2 * half + jj;
-                uint32_t v[32];
-                tc_ld32(t_lane + kUColS + 32 * j, v);
-                tc_wait_ld();
+                uint32_t (&v)[32] = sv[jj];
                 if (nvalid == kUTile) {                        // full tile: no per-key bound checks
                     float t0 = tmax, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
 #pragma unroll
@@ -511,12 +530,10 @@ __global__ void __launch_bounds__(kUThreads, 1) qattn_umma_kernel(AttnArgs a, in
                     tc_wait_st();
                 }
             }
-#pragma unroll 1
+#pragma unroll
             for (int jj = 0; jj < 2; ++jj) {
                 const int j = 2 * half + jj;
-                uint32_t v[32];
-                tc_ld32(t_lane + kUColS + 32 * j, v);
-                tc_wait_ld();
+                uint32_t (&v)[32] = sv[jj];                    // the scores are still in registers from the first pass
                 uint32_t pk[16];
                 if (nvalid == kUTile) {                        // full tile; unused columns carry the maximum +inf: weights 0
                     const float mneg = col_on ? -m_run : -INFINITY;
