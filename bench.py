@@ -608,7 +608,7 @@ def run_criteo(args):
 
 def run_mtok(args):
     """Attention of 32 query tokens per user (128 query columns per kv head) over a 2,048-key packed cache: the
-    tcgen05 kernel (default for 56 or more columns) and the warp-level kernel (eight columns per tile) on the same
+    tcgen05 kernel (default for 49 or more columns) and the warp-level kernel (eight columns per tile) on the same
     inputs.  Single GPU, reporting only."""
     from omnistack_rs_b200 import _lib
     from omnistack_rs_b200.kernels.fused_attention import omni_attn

@@ -347,9 +347,9 @@ static KernelChoice kernel_choice_from_env() {
 }
 
 // Query columns per kv head from which the tcgen05 kernel is taken: it dequantises a key once for up to 128 columns,
-// the warp-level kernel once per eight (measured, 64 users x 2,048 keys: 48 columns 0.280 vs 0.236 ms, 56 columns
-// 0.281 vs 0.303 ms, 128 columns 0.293 vs 0.550 ms).
-constexpr int64_t kUmmaMinColumns = 56;
+// the warp-level kernel once per eight (measured, 64 users x 2,048 keys: 48 columns = six tiles 0.246 vs 0.235 ms,
+// 56 columns = seven tiles 0.247 vs 0.303 ms, 128 columns 0.259 vs 0.546 ms).
+constexpr int64_t kUmmaMinColumns = 49;
 
 // Which tensor-core kernel serves a call, if any (otherwise the lane-per-key kernel does).
 // Measured crossover: the warp-level kernel wins from 128 keys on, and for shorter caches once the lane-per-key

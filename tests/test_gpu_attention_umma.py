@@ -67,7 +67,7 @@ def test_umma_ragged_rotation_and_scale(dev):
 
 
 def test_umma_is_the_default_for_many_columns(dev, monkeypatch):
-    """Without the override the tcgen05 kernel serves calls with 56 or more query columns per kv head and agrees
+    """Without the override the tcgen05 kernel serves calls with 49 or more query columns per kv head and agrees
     with the warp-level kernel that would otherwise serve them tile by tile."""
     fa = attn_mod()
     kn, kq, kr, vn, cb, gen = make_cache(2, 2, 700, seed=9, user_id=6)
