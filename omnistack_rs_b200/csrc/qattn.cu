@@ -20,6 +20,8 @@ namespace omni {
 
 constexpr int kAttnWarps = 4;
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];\n" :: "l"(p)); }
+
 template <int DT>
 __global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(AttnArgs a) {
     __shared__ __align__(16) float q_s[kAttnWarps][kHeadDim];
@@ -102,6 +104,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32) qattn_lane_per_key_kernel(Att
     for (int64_t k = s0 + lane; k < s1; k += 32) {
         const int64_t row = base_row + k;
         const uint4* kp = reinterpret_cast<const uint4*>(a.k_nib + row * kNibBytes);
+        // This key's sign bytes, norm and V row are needed one after the other further down: on a cold cache that is
+        // three memory latencies in a row, so they are requested now, together with the K and V rows of the lane's
+        // next key (a V row in the pair layout lies in this key's row and its partner's: the same 512-byte group).
+        prefetch_l2(a.v_nib + row * kNibBytes);
+        if (a.v_paired && k < (len & ~(int64_t)7)) prefetch_l2(a.v_nib + (base_row + (k ^ 3)) * kNibBytes);
+        if (a.with_qjl) { prefetch_l2(a.k_qjl + row * kQjlBytes); prefetch_l2(a.k_norms + row); }
+        if (k + 32 < s1) { prefetch_l2(a.k_nib + (row + 32) * kNibBytes); prefetch_l2(a.v_nib + (row + 32) * kNibBytes); }
         float dot = 0.f;
 #pragma unroll
         for (int c4 = 0; c4 < 4; ++c4) {
