@@ -321,7 +321,7 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
     verify = None
     if with_verify:
         verify = verify_against_oracle(dev, rank, world, users, Hq, qs[0], ref_out, k_nib, k_qjl, k_norms, v_nib, cb,
-                                       slots, lens_dev)
+                                       slots, lens_dev, n_check=min(args.verify_users, users))
 
     # ---- CPU baseline: the oracle on a few users of the same shape (rank 0, N = 1) ------
     cpu = None
@@ -797,6 +797,7 @@ def main():
     ap.add_argument("--chunks", type=int, default=None, help="user chunks of the pipelined host-buffer step (default: by batch)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-verify", action="store_true", help="skip the oracle check of gathered sample users")
+    ap.add_argument("--verify-users", type=int, default=64, help="users per rank recomputed by the CPU oracle after the timed loops")
     ap.add_argument("--no-secondary", action="store_true", help="default workload only: skip the other configurations")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--ref-users", type=int, default=2, help="users per step of the reference arm")
