@@ -176,6 +176,7 @@ def verify_against_oracle(dev, rank, world, users, Hq, q, out, k_nib, k_qjl, k_n
     import torch.distributed as dist
     from omnistack_rs_b200.serving import gather_rows_to_rank0
     from omnistack_rs_b200.kernels.fused_attention import pair_v_rows
+    t_start = time.perf_counter()
     g = torch.Generator().manual_seed(100 + rank)
     picks = sorted({0, users - 1, *torch.randint(0, users, (max(n_check - 2, 0),), generator=g).tolist()})
     while len(picks) < min(n_check, users):
@@ -197,18 +198,21 @@ def verify_against_oracle(dev, rank, world, users, Hq, q, out, k_nib, k_qjl, k_n
     if rank != 0:
         return None
     import oracle as orc
-    use_all_host_threads()
+    t_gathered = time.perf_counter()
+    threads = use_all_host_threads()
     cbc = cb.cpu()
+    sample = {k: v.cpu() for k, v in sample.items()}
     worst = 0.0
     for i in range(sample["out"].shape[0]):
         n = int(sample["len"][i])
         if n == 0:
             continue
-        want = orc.decode_attention(sample["q"][i:i + 1].cpu(), sample["kn"][i:i + 1, :, :n].cpu(),
-                                    sample["kq"][i:i + 1, :, :n].cpu(), sample["kr"][i:i + 1, :, :n].cpu(),
-                                    sample["vn"][i:i + 1, :, :n].cpu(), cbc, 0)
-        worst = max(worst, float((sample["out"][i:i + 1].cpu() - want).abs().max()))
+        want = orc.decode_attention(sample["q"][i:i + 1], sample["kn"][i:i + 1, :, :n], sample["kq"][i:i + 1, :, :n],
+                                    sample["kr"][i:i + 1, :, :n], sample["vn"][i:i + 1, :, :n], cbc, 0)
+        worst = max(worst, float((sample["out"][i:i + 1] - want).abs().max()))
     return {"users_checked": int(sample["out"].shape[0]), "max_abs_err": worst, "tolerance": 3e-3,
+            "seconds": {"gather": round(t_gathered - t_start, 2), "oracle": round(time.perf_counter() - t_gathered, 2)},
+            "host_threads": threads,
             "ok": bool(worst <= 3e-3 and torch.isfinite(checksum).all()), "ranks": world,
             "checksum_rows_gathered": int(checksum.shape[0]), "transport": "nccl gather" if world > 1 else "local"}
 
@@ -224,6 +228,7 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
     if args.users and workload == args.workload:
         users = args.users
     scale = 1.0 / math.sqrt(128)
+    wall = {"start": time.perf_counter()}
 
     # ---- resident cache ------------------------------------------------------------
     bytes_per_user = Hkv * S * BYTES_PER_KEY
@@ -263,6 +268,8 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
     flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev) if small else None
 
     # ---- device-resident timing ------------------------------------------------------
+    torch.cuda.synchronize(dev)
+    wall["cache_built"] = time.perf_counter()
     for i in range(warmup):
         step(i)
     barrier()
@@ -294,6 +301,7 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
     checksum = float(out.float().abs().mean())
 
     # ---- end to end: host query in, host result out -----------------------------------
+    wall["device_loop_done"] = time.perf_counter()
     host = HostDecodeStep(k_nib, k_qjl, k_norms, v_nib, cb, n_heads=Hq, batch=users, q_dtype=torch.bfloat16,
                           user_id=0, seq_lens=lens_dev, cache_slots=slots, scale=scale,
                           n_chunks=args.chunks if workload == args.workload else None, v_paired=PAIR_V)
@@ -318,10 +326,11 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
     e2e_ok = bool((res - ref_out.cpu()).abs().max() <= 1.5e-3)   # splits round their fp16 softmax weights against other maxima
     _lib.check_device_status(dev)
 
+    wall["host_loop_done"] = time.perf_counter()
     verify = None
     if with_verify:
         verify = verify_against_oracle(dev, rank, world, users, Hq, qs[0], ref_out, k_nib, k_qjl, k_norms, v_nib, cb,
-                                       slots, lens_dev, n_check=min(args.verify_users, users))
+                                       slots, lens_dev, n_check=max(1, min(args.verify_users, users)))
 
     # ---- CPU baseline: the oracle on a few users of the same shape (rank 0, N = 1) ------
     cpu = None
@@ -353,6 +362,10 @@ def measure_decode(args, workload, dev, rank, world, local, steps, warmup, with_
                              if host.mode == "direct" else "staged copies pipelined over user chunks"),
                 "matches_device_path": e2e_ok},
         "verify": verify,
+        "wall_seconds": {"cache_build": round(wall["cache_built"] - wall["start"], 2),
+                         "device_loop": round(wall["device_loop_done"] - wall["cache_built"], 2),
+                         "host_buffer_loop": round(wall["host_loop_done"] - wall["device_loop_done"], 2),
+                         "verify_and_cpu": round(time.perf_counter() - wall["host_loop_done"], 2)},
         "gpu_launches": steps * launches,
         "clocks": clocks, "checksum": checksum,
     }
@@ -393,12 +406,17 @@ def run_ours(args):
         print(json.dumps(line))
 
 
-def use_all_host_threads():
-    """torchrun exports OMP_NUM_THREADS=1; the CPU legs are meant to use every core they may."""
+def use_all_host_threads(peers_waiting=True):
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs are meant to use every core they may.  With several ranks one
+    core per rank is left alone: the ranks that wait for rank 0 spin on theirs, and an OpenMP team that shares a core
+    with a spinning thread loses a scheduler quantum at every barrier (measured: 8 s instead of 0.1 s per user)."""
     try:
         n = len(os.sched_getaffinity(0))
     except AttributeError:
         n = os.cpu_count() or 1
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and peers_waiting:
+        n -= world
     torch.set_num_threads(max(1, n))
     return torch.get_num_threads()
 
@@ -756,7 +774,7 @@ def run_reference(args):
     if rank != 0:
         return
     import oracle as orc
-    use_all_host_threads()
+    use_all_host_threads(peers_waiting=False)             # the other ranks have exited
     desc, Hq, Hkv, S, users = WORKLOADS[args.workload]
     n_users = args.ref_users
     gen = torch.Generator().manual_seed(7)
