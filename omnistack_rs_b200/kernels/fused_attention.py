@@ -189,8 +189,9 @@ def clear_prepared_calls() -> None:
 
 
 def _plan_key(q, tensors, user_id, scale, flags, n_splits, lora):
-    return (tuple(id(t) for t in tensors), q.shape, q.dtype, user_id if not isinstance(user_id, torch.Tensor) else None,
-            scale, flags, n_splits, None if lora is None else float(lora[4]))
+    return (tuple(id(t) for t in tensors), tensors[0].shape, q.shape, q.dtype,
+            user_id if not isinstance(user_id, torch.Tensor) else None, scale, flags, n_splits,
+            None if lora is None else float(lora[4]))
 
 
 def _build_call(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl, seq_lens, cache_slots,
@@ -272,7 +273,7 @@ def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, w
                 break
         else:
             return hit.run(q, lora)
-        del _PLANS[key]
+        _PLANS.pop(key, None)
     call, keepable = _build_call(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, with_qjl, seq_lens,
                                  cache_slots, rotate_q, unrotate_out, n_splits, lora, v_paired)
     out = call.run(q, lora)
@@ -283,7 +284,7 @@ def _qattn(q, k_nibbles, k_qjl, k_norms, v_nibbles, codebooks, user_id, scale, w
         if call.lora_const is not None:                     # nor the adapter stacks: re-read through the weak references
             call.lora_const = (None, None) + call.lora_const[2:]
         if len(_PLANS) >= _MAX_PLANS:
-            del _PLANS[next(iter(_PLANS))]
+            _PLANS.pop(next(iter(_PLANS)), None)
         _PLANS[key] = call
     return out
 

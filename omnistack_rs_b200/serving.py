@@ -245,6 +245,16 @@ class GraphedAttention:
                  lora_a=None, lora_b=None, lora_alpha: float = 1.0, **attn_kwargs):
         from .kernels.fused_attention import omni_attn
         dev = _lib.require_cuda(k_nibbles, k_qjl, k_norms, v_nibbles)
+        # a replay reads the addresses the capture saw: an argument the call would have to convert (other device,
+        # dtype or layout) would be captured as a temporary copy, so every tensor must already be in its final form
+        final = [("k_nibbles", k_nibbles, torch.uint8), ("k_qjl", k_qjl, torch.uint8), ("k_norms", k_norms, torch.float32),
+                 ("v_nibbles", v_nibbles, torch.uint8), ("codebooks", codebooks, torch.float32),
+                 ("lora_a", lora_a, torch.float32), ("lora_b", lora_b, torch.float32),
+                 ("seq_lens", attn_kwargs.get("seq_lens"), torch.int32), ("cache_slots", attn_kwargs.get("cache_slots"), torch.int32),
+                 ("user_id", user_id if isinstance(user_id, torch.Tensor) else None, torch.int32)]
+        for name, t, dt in final:
+            if t is not None and not (t.device == dev and t.dtype is dt and t.is_contiguous()):
+                raise ValueError(f"GraphedAttention: {name} must be a contiguous {dt} tensor on {dev}")
         B, _, T, _ = q_shape
         self.q = torch.zeros(q_shape, dtype=q_dtype, device=dev)
         self.x = self.lora_indices = None
