@@ -128,15 +128,16 @@ def wht128(x: torch.Tensor) -> torch.Tensor:
     if x.shape[-1] != HEAD_DIM:
         raise ValueError(f"rotation needs last dim = {HEAD_DIM} (head_dim), got {x.shape[-1]}")
     a = x.detach().to(torch.float32).reshape(-1, HEAD_DIM).clone()
+    b = torch.empty_like(a)                       # the stages ping-pong between two buffers
     n = a.shape[0]
     h = 1
     while h < HEAD_DIM:
-        v = a.view(n, HEAD_DIM // (2 * h), 2, h)
-        up = v[:, :, 0, :] + v[:, :, 1, :]
-        lo = v[:, :, 0, :] - v[:, :, 1, :]
-        a = torch.stack((up, lo), dim=2).reshape(n, HEAD_DIM)
+        va, vb = a.view(n, HEAD_DIM // (2 * h), 2, h), b.view(n, HEAD_DIM // (2 * h), 2, h)
+        torch.add(va[:, :, 0, :], va[:, :, 1, :], out=vb[:, :, 0, :])
+        torch.sub(va[:, :, 0, :], va[:, :, 1, :], out=vb[:, :, 1, :])
+        a, b = b, a
         h *= 2
-    return (a * WHT_SCALE).reshape(x.shape).to(x.dtype)
+    return a.mul_(WHT_SCALE).reshape(x.shape).to(x.dtype)
 
 
 # --------------------------------------------------------------------------- #
