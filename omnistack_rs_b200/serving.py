@@ -136,6 +136,9 @@ class QuantizedKVCache:
         # converts the groups of eight keys it completes (``v_nib`` is then not interchangeable with the reference's)
         self.pair_v = bool(pair_v)
         self.lens = torch.zeros(n_users, dtype=torch.int64, device=self.device)
+        # the same lengths as the attention entry points take them (int32, same storage for the cache's lifetime, so
+        # repeated ``attend`` calls reuse one prepared call)
+        self.lens32 = torch.zeros(n_users, dtype=torch.int32, device=self.device)
         self.user_ids = (torch.arange(n_users, dtype=torch.int32, device=self.device) if user_ids is None
                          else user_ids.to(device=self.device, dtype=torch.int32).contiguous())
 
@@ -155,6 +158,7 @@ class QuantizedKVCache:
         if self.pair_v:
             pair_v_rows(self.v_nib, self.lens, self.lens + T)
         self.lens += T
+        self.lens32.copy_(self.lens)
 
     def attend(self, q: torch.Tensor, scale: Optional[float] = None, with_qjl: bool = True,
                rotate_q: bool = False, unrotate_out: bool = False, n_splits: Optional[int] = None) -> torch.Tensor:
@@ -162,7 +166,7 @@ class QuantizedKVCache:
         if scale is None:
             scale = 1.0 / math.sqrt(HEAD_DIM)
         return _qattn(q, self.k_nib, self.k_qjl, self.k_norms, self.v_nib, self.codebooks, self.user_ids, scale,
-                      with_qjl, seq_lens=self.lens, rotate_q=rotate_q, unrotate_out=unrotate_out, n_splits=n_splits,
+                      with_qjl, seq_lens=self.lens32, rotate_q=rotate_q, unrotate_out=unrotate_out, n_splits=n_splits,
                       v_paired=self.pair_v)
 
 
