@@ -1,0 +1,80 @@
+"""Size-independent properties of the CPU oracle's codec (the same properties the GPU tests use at full size):
+pack / unpack inverses, the rotation's involution and norm preservation, the nearest-centroid rule, the bound on the
+reconstruction error, and the effect of the QJL term.  Randomised over shapes and seeds with hypothesis."""
+import math
+
+import torch
+from hypothesis import given, settings, strategies as st
+
+import oracle as orc
+from oracle import omni_oracle as oo
+
+CB = torch.tensor([-2.733, -2.069, -1.618, -1.256, -0.9424, -0.6568, -0.3881, -0.1284,
+                   0.1284, 0.3881, 0.6568, 0.9424, 1.256, 1.618, 2.069, 2.733])
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.integers(1, 40), st.integers(0, 2 ** 31 - 1))
+def test_pack_unpack_are_inverses(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    codes = torch.randint(0, 16, (n, 128), generator=g, dtype=torch.uint8)
+    assert torch.equal(oo.unpack_nibbles(oo.pack_nibbles(codes)), codes)
+    bits = torch.rand(n, 64, generator=g) > 0.5
+    assert torch.equal(oo.unpack_sign_bits(oo.pack_sign_bits(bits)) > 0.5, bits)
+
+
+@settings(max_examples=20, deadline=None)
+@given(st.integers(1, 30), st.integers(0, 2 ** 31 - 1), st.sampled_from([1e-3, 1.0, 37.0]))
+def test_rotation_is_an_isometric_involution(n, seed, scale):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, 128, generator=g) * scale
+    y = orc.wht128(x)
+    assert torch.allclose(orc.wht128(y), x, rtol=0, atol=2e-6 * scale * 12)          # H/sqrt(128) is its own inverse
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), rtol=1e-5)
+    a, b = x[: n // 2 + 1], torch.flip(x, dims=[0])[: n // 2 + 1]
+    assert torch.allclose((orc.wht128(a) * orc.wht128(b)).sum(-1), (a * b).sum(-1), rtol=0, atol=1e-3 * scale * scale)
+
+
+@settings(max_examples=15, deadline=None)
+@given(st.integers(1, 6), st.integers(1, 3), st.integers(1, 20), st.integers(0, 5000), st.integers(0, 2 ** 31 - 1))
+def test_codec_round_trip_properties(B, H, T, user_id, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = orc.wht128(torch.randn(B, H, T, 128, generator=g))
+    nib, qjl, nrm = orc.quantize_heads(x, CB, user_id)
+    assert nib.shape == (B, H, T, 64) and qjl.shape == (B, H, T, 8) and nrm.shape == (B, H, T)
+    # the code is the nearest centroid: no other centroid is strictly closer
+    codes = oo.unpack_nibbles(nib.reshape(-1, 64)).reshape(B, H, T, 128).long()
+    chosen = (x - CB[codes]).abs()
+    assert bool((chosen.unsqueeze(-1) <= (x.unsqueeze(-1) - CB).abs() + 0.0).all())
+    # the stored norm is the residual's norm, and INT4-only reconstruction errs by exactly that much
+    plain = orc.dequantize_heads(nib, qjl, nrm, CB, user_id, with_qjl=False)
+    assert torch.allclose((x - plain).norm(dim=-1), nrm, rtol=1e-5, atol=1e-6)
+    # the QJL term moves the reconstruction towards x on average (reference: >= 5 % lower MSE on Gaussian data)
+    full = orc.dequantize_heads(nib, qjl, nrm, CB, user_id, with_qjl=True)
+    if B * H * T >= 24:
+        assert float(((x - full) ** 2).mean()) < float(((x - plain) ** 2).mean())
+    # seeds alias modulo 1024 and differ between heads
+    nib2, qjl2, _ = orc.quantize_heads(x, CB, user_id + 1024)
+    assert torch.equal(qjl2, qjl) and torch.equal(nib2, nib)
+    if H > 1:
+        assert not torch.equal(orc.quantize_heads(x[:, :1], CB, user_id)[1], orc.quantize_heads(x[:, 1:2], CB, user_id)[1]) \
+            or torch.equal(x[:, :1], x[:, 1:2])
+
+
+@settings(max_examples=10, deadline=None)
+@given(st.integers(1, 3), st.integers(1, 60), st.integers(0, 2 ** 31 - 1))
+def test_attention_is_a_convex_combination_of_value_rows(B, S, seed):
+    g = torch.Generator().manual_seed(seed)
+    K = orc.wht128(torch.randn(B, 2, S, 128, generator=g))
+    V = orc.wht128(torch.randn(B, 2, S, 128, generator=g))
+    kn, kq, kr = orc.quantize_heads(K, CB, 7)
+    vn, _, _ = orc.quantize_heads(V, CB, 7)
+    q = torch.randn(B, 4, 1, 128, generator=g)
+    out = orc.decode_attention(q, kn, kq, kr, vn, CB, 7)
+    v_hat = orc.dequantize_heads(vn, torch.zeros_like(kq), torch.zeros_like(kr), CB, 7, with_qjl=False)
+    lo = v_hat.min(dim=2).values.repeat_interleave(2, dim=1).unsqueeze(2)
+    hi = v_hat.max(dim=2).values.repeat_interleave(2, dim=1).unsqueeze(2)
+    assert bool(((out >= lo - 1e-5) & (out <= hi + 1e-5)).all())
+    # scaling the query by zero gives the plain mean of the value rows
+    mean = orc.decode_attention(torch.zeros_like(q), kn, kq, kr, vn, CB, 7)
+    assert torch.allclose(mean, v_hat.mean(dim=2).repeat_interleave(2, dim=1).unsqueeze(2), atol=1e-5)
